@@ -40,6 +40,7 @@ struct DirFamily { const char *architecture; DirCreate create; const char *unit;
 const DirFamily kDirFamilies[] = {
     {"Famudra", nb_family_layered_create, "layered.cu"},
     {"Rakarax", nb_family_layered_create, "layered.cu"},
+    {"Gokinex", nb_family_layered_create, "layered.cu"},
 };
 }  // namespace
 

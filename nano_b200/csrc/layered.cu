@@ -7,6 +7,11 @@
 // "retention" (rotary linear attention with a fixed decay per head, fp32 state) and "parallel" (a sliding-window grouped-query
 // attention whose scores are mixed across heads, side by side with a Mamba selective scan, summed with fixed scales); feed-forward
 // "dense" (PolyNorm activation); a layer may use another layer's weights ("weights_of") with cache and state of its own.
+// "Gokinex" -- the same sequential form with Dynamic-Tanh norms (tanh(alpha u) w + b); the token row times a fixed scale plus a
+// hashed row for the (previous, current) token pair; mixers "attention" (grouped-query differential attention: two softmax maps per
+// head over the same values, rotary positions on interleaved pairs with frequencies rescaled by wavelength, optionally on another
+// layer's keys and values) and "mamba2" (state-space duality with a scalar decay per head and token); feed-forward "dense" (gated
+// gelu) or "moe" (silu experts chosen by sigmoid scores that weight the expert's input, plus a shared expert behind a sigmoid gate).
 // "Famudra" -- parallel layers  x <- x + (mixer(shift(norm1 x)) + ff(norm2 x))  with scalar-gain RMS norms and a
 // token shift on the mixer input; mixers "rglru" (gelu branch x conv + real-gated linear recurrent unit) and "latent_attention"
 // (queries and keys/values through normed low-rank latents, no positions, causal softmax); feed-forward "moe" (top-k routed
@@ -39,6 +44,7 @@
 #include "family.h"
 #include "layered_kernels.cuh"
 #include "layered_mixers.cuh"
+#include "layered_mixers2.cuh"
 #include "modeldir.h"
 #include "sample_host.h"
 
@@ -51,11 +57,13 @@ namespace {
 
 struct Weight { void *p = nullptr; uint32_t rows = 0, cols = 0; };
 
-enum MixerType { MIX_RGLRU = 0, MIX_LATENT_ATTN = 1, MIX_RETENTION = 2, MIX_WINDOW_SSM = 3 };
+enum MixerType { MIX_RGLRU = 0, MIX_LATENT_ATTN = 1, MIX_RETENTION = 2, MIX_WINDOW_SSM = 3, MIX_DIFF_ATTN = 4, MIX_SSD = 5 };
 // how a layer combines its sublayers: Famudra's parallel form with a token shift and scalar-gain norms, or sequential sublayers
 // between an input norm and an output norm each (vector gains stored around zero)
 enum LayerForm { FORM_PARALLEL_SHIFT = 0, FORM_SANDWICH = 1 };
-enum FfKind { FF_NONE = 0, FF_MOE = 1, FF_DENSE_POLY = 2 };
+enum FfKind { FF_NONE = 0, FF_MOE = 1, FF_DENSE_POLY = 2, FF_DENSE_GLU = 3, FF_MOE_SCORED = 4 };
+// the norms of the sequential form: unit RMS times a vector gain stored around zero, or Dynamic Tanh
+enum NormKind { NORM_RMS_ZERO = 0, NORM_DYT = 1 };
 
 struct Layer {
     int type = 0;
@@ -79,6 +87,15 @@ struct Layer {
     uint32_t mC = 0, mN = 0, mR = 0, m_taps = 0;
     float *m_conv = nullptr, *m_conv_b = nullptr, *dt_b = nullptr, *A = nullptr, *Dv = nullptr;
     Weight xw, dtw, mo; float *dt_wf = nullptr;      // dt_wf: the step-size projection once more in fp32, for the scan that makes dt itself
+    // Dynamic-Tanh norms of the sequential form
+    Dyt d1{}, d1b{}, d2{}, d2b{};
+    // differential attention: proj = [q | k | v] with its biases (q alone when the keys and values are layer kv_from's); H, G, dim, vdim,
+    // scale, rot_dims, rot_tab, RL as above; lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff
+    int kv_from = -1; float diff = 0.0f, lambda = 0.0f; float *proj_b = nullptr, *o_b = nullptr;
+    uint32_t a_hpb = 0, a_ngk = 0, a_qt = 0;      // heads per attention block, kv heads such a block stages, query tokens per prefill block
+    // state-space duality: proj = [z | x | B | C | dt]; H heads of vdim, mN states, G groups, m_taps, m_conv, m_conv_b, dt_b, A = exp(A_log)
+    // per head, Dv per head; the output is normed in `parts` equal parts with the gain gn
+    uint32_t parts = 0; float *gn = nullptr;
     // feed-forward
     int ff_kind = FF_NONE; float *act = nullptr;
     bool has_mlp = false, has_shared = false;
@@ -123,6 +140,10 @@ struct LayeredEngine : nb::EngineBase {
     uint32_t *b_tick = nullptr;      // attention: tickets of the key splits
     uint32_t *b_idx = nullptr, *b_cnt = nullptr, *b_off = nullptr, *b_fill = nullptr, *b_slot = nullptr, *b_rows = nullptr;
     float *b_xn = nullptr, *logits = nullptr, *keep = nullptr;
+    // Dynamic-Tanh designs: embedding scale, the pair table and its hash, the norms around the stack, where a slot keeps the last token
+    int norm_kind = NORM_RMS_ZERO; float emb_scale = 1.0f; Weight pairs; uint32_t buckets = 0, mul_prev = 0, mul_cur = 0; Dyt embed_norm{}, final_dyt{}; size_t st_tok = 0;
+    std::vector<std::pair<std::string, float2 *>> rot_tabs;      // position tables of the rotary attention layers, one per distinct setting
+    float *b_dpart = nullptr, *b_sseg = nullptr, *b_sdx = nullptr, *b_sdy = nullptr, *b_f2 = nullptr, *b_hg = nullptr, *b_sh2 = nullptr, *b_sg = nullptr, *b_wrow = nullptr; uint32_t *b_dtick = nullptr;
     uint32_t *ids_dev = nullptr, *want_dev = nullptr, *next_dev = nullptr, *tok_host = nullptr; uint8_t *seen = nullptr;
     uint32_t last_T = 0;
     uint32_t *dpos = nullptr, *zero_dev = nullptr;            // device-side position of a captured decode step; a constant 0
@@ -386,6 +407,153 @@ int load_dense(Loader &ld, const nb::Json *f, const std::string &p, Layer *L, ui
     return ld.vec(p + "act", {4}, &L->act);
 }
 
+// Dynamic-Tanh norm `name`: gain, bias `name`.b, one number `name`.alpha
+int load_dyt(Loader &ld, const std::string &name, uint32_t E, Dyt *n) {
+    float *w = nullptr, *b = nullptr; std::vector<float> al; std::vector<uint64_t> sh; int r;
+    if ((r = ld.vec(name, {E}, &w)) || (r = ld.vec(name + ".b", {E}, &b)) || (r = ld.host_f32(name + ".alpha", &al, &sh)) || (r = ld.expect(name + ".alpha", sh, {}))) return r;
+    n->w = w; n->b = b; n->alpha = al[0];
+    return 0;
+}
+
+// names[i] are vectors of lens[i] numbers; joined into one fp32 vector
+int joined_vec(Loader &ld, const std::vector<std::string> &names, const std::vector<uint64_t> &lens, float **dst) {
+    std::vector<float> all;
+    for (size_t i = 0; i < names.size(); i++) {
+        std::vector<float> h; std::vector<uint64_t> sh; int r;
+        if ((r = ld.host_f32(names[i], &h, &sh)) || (r = ld.expect(names[i], sh, {lens[i]}))) return r;
+        all.insert(all.end(), h.begin(), h.end());
+    }
+    return ld.put_f32(all, dst);
+}
+
+// (cos, sin) of position x frequency for `positions` positions, built in double.  f_i = base^(-2i/dims), rescaled by wavelength
+// l = 2 pi / f when `scaling` {factor, low, high, original} is given: kept where l < original / high, divided by factor where
+// l > original / low, and between the two blended, (1 - s) f / factor + s f with s = (original / l - low) / (high - low).
+int rope_table(Loader &ld, const nb::Json *rot, const std::string &p, uint32_t dims, uint32_t positions, float2 **out) {
+    double base, factor = 1.0, low = 0.0, high = 0.0, original = 0.0;
+    if (!rot->number("base", &base) || !(base > 0.0)) return fail(NB200_EINVAL, "%s: rot needs a base > 0", p.c_str());
+    const nb::Json *sc = rot->present("scaling") ? rot->get("scaling") : nullptr;
+    if (sc && (!sc->number("factor", &factor) || !sc->number("low", &low) || !sc->number("high", &high) || !sc->number("original", &original) || !(factor > 0.0) || !(high > low) || !(original > 0.0)))
+        return fail(NB200_EINVAL, "%s: rot.scaling needs factor > 0, low < high and original > 0", p.c_str());
+    char key[160];
+    snprintf(key, sizeof key, "%u/%.17g/%d/%.17g/%.17g/%.17g/%.17g", dims, base, sc ? 1 : 0, factor, low, high, original);
+    for (auto &kv : ld.e->rot_tabs) if (kv.first == key) { *out = kv.second; return 0; }
+    const uint32_t half = dims / 2u;
+    const double two_pi = 6.283185307179586476925286766559;
+    std::vector<float> tab((size_t)positions * half * 2);
+    for (uint32_t i = 0; i < half; i++) {
+        double f = pow(base, -2.0 * (double)i / (double)dims);
+        if (sc) {
+            const double wave = two_pi / f;
+            if (wave > original / low) f = f / factor;
+            else if (!(wave < original / high)) { const double sm = (original / wave - low) / (high - low); f = (1.0 - sm) * f / factor + sm * f; }
+        }
+        for (uint32_t q = 0; q < positions; q++) { const double a = (double)q * f; tab[((size_t)q * half + i) * 2] = (float)cos(a); tab[((size_t)q * half + i) * 2 + 1] = (float)sin(a); }
+    }
+    float *t = nullptr; int r;
+    if ((r = ld.put_f32(tab, &t))) return r;
+    *out = reinterpret_cast<float2 *>(t);
+    ld.e->rot_tabs.emplace_back(key, *out);
+    return 0;
+}
+
+constexpr size_t kDiffSmemMax = 200 * 1024;
+// grouped-query differential attention; `layers` lets a layer with kv_from check the layer it reads
+int load_diff_attn(Loader &ld, const nb::Json *m, const std::string &p, Layer *L, uint32_t E, uint32_t positions, const std::vector<Layer> &layers, uint32_t self_index) {
+    double sc, diff;
+    if (!u32_of(m, "heads", &L->H) || !u32_of(m, "kv_heads", &L->G) || !u32_of(m, "dim", &L->dim) || !u32_of(m, "vdim", &L->vdim) || !m->number("scale", &sc) || !m->number("diff", &diff))
+        return fail(NB200_EINVAL, "%s: an attention mixer needs heads, kv_heads, dim, vdim, scale and diff", p.c_str());
+    L->scale = (float)sc; L->diff = (float)diff;
+    if (!L->H || !L->G || L->H % L->G || !L->dim || !L->vdim) return fail(NB200_EINVAL, "%s: heads %u / kv_heads %u / dim %u / vdim %u unusable", p.c_str(), L->H, L->G, L->dim, L->vdim);
+    if (L->vdim > 256) return fail(NB200_EINVAL, "%s: vdim %u above 256 has no attention kernel", p.c_str(), L->vdim);
+    const uint64_t H = L->H, G = L->G, D = L->dim, VD = L->vdim;
+    int r;
+    if (m->present("rot")) {
+        const nb::Json *rot = m->get("rot");
+        if (!u32_of(rot, "dims", &L->rot_dims) || L->rot_dims > L->dim || (L->rot_dims & 1u)) return fail(NB200_EINVAL, "%s: rot needs an even dims <= dim", p.c_str());
+        if (L->rot_dims && (r = rope_table(ld, rot, p, L->rot_dims, positions, &L->rot_tab))) return r;
+    }
+    L->RL = (uint32_t)((G * 2 * D + G * VD + 3u) & ~(uint64_t)3u);
+    if (m->present("kv_from")) {
+        uint32_t j = 0;
+        if (!u32_of(m, "kv_from", &j) || j >= self_index || layers[j].type != MIX_DIFF_ATTN || layers[j].kv_from >= 0)
+            return fail(NB200_EINVAL, "%s: kv_from must name an earlier attention layer with keys and values of its own", p.c_str());
+        const Layer &S = layers[j];
+        if (S.G != L->G || S.dim != L->dim || S.vdim != L->vdim || S.rot_dims != L->rot_dims || S.rot_tab != L->rot_tab) return fail(NB200_EINVAL, "%s: layer %u's keys and values have another shape or rotation", p.c_str(), j);
+        L->kv_from = (int)j;
+        if ((r = ld.stacked({p + "q"}, {H * 2 * D}, E, &L->proj)) || (r = ld.vec(p + "q.b", {H * 2 * D}, &L->proj_b))) return r;
+    } else if ((r = ld.stacked({p + "q", p + "k", p + "v"}, {H * 2 * D, G * 2 * D, G * VD}, E, &L->proj)) ||
+               (r = joined_vec(ld, {p + "q.b", p + "k.b", p + "v.b"}, {H * 2 * D, G * 2 * D, G * VD}, &L->proj_b))) return r;
+    {   // one number for the layer: exp(lq1 . lk1) - exp(lq2 . lk2) + diff
+        std::vector<float> v[4]; std::vector<uint64_t> sh; const char *nm[4] = {"lq1", "lk1", "lq2", "lk2"};
+        for (int i = 0; i < 4; i++) if ((r = ld.host_f32(p + nm[i], &v[i], &sh)) || (r = ld.expect(p + nm[i], sh, {D}))) return r;
+        double s1 = 0.0, s2 = 0.0;
+        for (uint64_t i = 0; i < D; i++) { s1 += (double)v[0][i] * v[1][i]; s2 += (double)v[2][i] * v[3][i]; }
+        L->lambda = (float)(exp(s1) - exp(s2) + diff);
+    }
+    if ((r = ld.stacked({p + "o"}, {E}, H * VD, &L->o)) || (r = ld.vec(p + "o.b", {E}, &L->o_b))) return r;
+    // the widest block (heads per block, query tokens per prefill block) whose key and value slices fit the shared memory
+    const bool vec = diff_attn_vec(L->dim, L->vdim, (uint32_t)(H * 2 * D + (L->kv_from < 0 ? G * 2 * D + G * VD : 0)));
+    for (uint32_t hpb = std::min<uint32_t>(8u, L->H); hpb >= 1u && !L->a_hpb; hpb = hpb / 2u) {
+        const uint32_t ngk = diff_attn_ngk(L->H, L->G, hpb);
+        for (uint32_t qt : {L->vdim <= 128u ? 8u : 4u, 4u, 1u})
+            if (diff_attn_smem(L->dim, L->vdim, ngk, qt, hpb, vec) <= kDiffSmemMax) { L->a_hpb = hpb; L->a_ngk = ngk; L->a_qt = qt; break; }
+    }
+    if (!L->a_hpb) return fail(NB200_EINVAL, "%s: one key page of a key/value head (%u + %u floats per key) does not fit the attention kernel's shared memory", p.c_str(), 2 * L->dim, L->vdim);
+    return 0;
+}
+
+int load_ssd(Loader &ld, const nb::Json *m, const std::string &p, Layer *L, uint32_t E) {
+    if (!u32_of(m, "heads", &L->H) || !u32_of(m, "vdim", &L->vdim) || !u32_of(m, "state", &L->mN) || !u32_of(m, "groups", &L->G) || !u32_of(m, "conv", &L->m_taps) || !u32_of(m, "norm_groups", &L->parts))
+        return fail(NB200_EINVAL, "%s: a mamba2 mixer needs heads, vdim, state, groups, conv and norm_groups", p.c_str());
+    if (!L->H || !L->vdim || !L->mN || !L->G || L->H % L->G || !L->m_taps || !L->parts || (L->H * L->vdim) % L->parts)
+        return fail(NB200_EINVAL, "%s: heads %u / vdim %u / state %u / groups %u / conv %u / norm_groups %u unusable", p.c_str(), L->H, L->vdim, L->mN, L->G, L->m_taps, L->parts);
+    if (L->mN > 256) return fail(NB200_EINVAL, "%s: state %u above 256 has no scan kernel", p.c_str(), L->mN);
+    const uint64_t Hn = L->H, inner = Hn * L->vdim, XW = inner + 2ull * L->G * L->mN;
+    int r;
+    if ((r = ld.stacked({p + "in"}, {inner + XW + Hn}, E, &L->proj)) || (r = ld.vec(p + "conv", {XW, L->m_taps}, &L->m_conv)) || (r = ld.vec(p + "conv.b", {XW}, &L->m_conv_b)) ||
+        (r = ld.vec(p + "dt_bias", {Hn}, &L->dt_b)) || (r = ld.vec(p + "D", {Hn}, &L->Dv)) || (r = ld.vec(p + "norm", {inner}, &L->gn)) || (r = ld.stacked({p + "o"}, {E}, inner, &L->o))) return r;
+    std::vector<float> al; std::vector<uint64_t> sh;
+    if ((r = ld.host_f32(p + "A_log", &al, &sh)) || (r = ld.expect(p + "A_log", sh, {Hn}))) return r;
+    for (float &v : al) v = (float)exp((double)v);          // the decay rate of a head: a_t = exp(-rate dt_t)
+    return ld.put_f32(al, &L->A);
+}
+
+// gated feed-forward down(act(gate h) x (up h)): up = [gate | up] stacked
+int load_glu_dense(Loader &ld, const nb::Json *f, const std::string &p, Layer *L, uint32_t E) {
+    if (!u32_of(f, "ff", &L->ff) || !L->ff) return fail(NB200_EINVAL, "%s: a dense feed-forward needs ff", p.c_str());
+    L->has_mlp = true; L->ff_kind = FF_DENSE_GLU;
+    int r;
+    if ((r = ld.stacked({p + "gate", p + "up"}, {L->ff, L->ff}, E, &L->up))) return r;
+    return ld.stacked({p + "down"}, {E}, L->ff, &L->down);
+}
+
+// mixture of gated silu experts chosen by sigmoid scores; the router matrix carries the shared expert's gate as one more row
+int load_moe_scored(Loader &ld, const nb::Json *f, const std::string &p, Layer *L, uint32_t E) {
+    if (!u32_of(f->get("router"), "experts", &L->NE) || !u32_of(f->get("router"), "top", &L->top) || !u32_of(f->get("expert"), "ff", &L->ff))
+        return fail(NB200_EINVAL, "%s: a moe feed-forward needs router.experts, router.top and expert.ff", p.c_str());
+    if (!L->NE || !L->top || L->top > L->NE || !L->ff) return fail(NB200_EINVAL, "%s: experts %u / top %u / ff %u unusable", p.c_str(), L->NE, L->top, L->ff);
+    L->has_mlp = true; L->ff_kind = FF_MOE_SCORED;
+    int r;
+    if (f->present("shared")) {
+        if (!u32_of(f->get("shared"), "ff", &L->sff) || !L->sff) return fail(NB200_EINVAL, "%s: shared.ff missing", p.c_str());
+        L->has_shared = true;
+        if ((r = ld.stacked({p + "shared.gate", p + "shared.up"}, {L->sff, L->sff}, E, &L->sup)) || (r = ld.stacked({p + "shared.down"}, {E}, L->sff, &L->sdown))) return r;
+    }
+    {
+        std::vector<float> all;
+        if ((r = append_rows(ld, p + "router", L->NE, E, 0, L->NE, &all)) || (L->has_shared && (r = append_rows(ld, p + "shared.sg", 1, E, 0, 1, &all))) || (r = ld.put_f32(all, &L->router))) return r;
+    }
+    std::vector<std::string> ups, downs; std::vector<uint64_t> ur, dr;
+    for (uint32_t i = 0; i < L->NE; i++) {
+        const std::string ep = p + "e" + std::to_string(i) + ".";
+        ups.push_back(ep + "gate"); ups.push_back(ep + "up"); ur.push_back(L->ff); ur.push_back(L->ff);
+        downs.push_back(ep + "down"); dr.push_back(E);
+    }
+    if ((r = ld.stacked(ups, ur, E, &L->up)) || (r = ld.stacked(downs, dr, L->ff, &L->down))) return r;
+    return 0;
+}
+
 // ---------------- launches ----------------
 template <typename A>
 int launch(LayeredEngine *e, void (*k)(const A), dim3 grid, dim3 block, size_t smem, const A &args) {
@@ -416,10 +584,13 @@ int gemm(LayeredEngine *e, GemmArgs a, uint32_t groups, uint32_t maxM, bool wf32
         const uint32_t gx = gemv_blocks(e, a.N, active ? std::min(active, groups) : groups);
         if (a.epi == EPI_CONV_RANGES)
             return f32 ? launch<GemmArgs>(e, k_gemv_ext<float, 1>, dim3(gx, groups), dim3(256), 0, a) : launch<GemmArgs>(e, k_gemv_ext<__nv_bfloat16, 1>, dim3(gx, groups), dim3(256), 0, a);
+        if (a.glu)
+            return f32 ? launch<GemmArgs>(e, k_gemv_ext<float, 3>, dim3(gx, groups), dim3(256), 0, a) : launch<GemmArgs>(e, k_gemv_ext<__nv_bfloat16, 3>, dim3(gx, groups), dim3(256), 0, a);
         if (a.a_poly)
             return f32 ? launch<GemmArgs>(e, k_gemv_ext<float, 2>, dim3(gx, groups), dim3(256), 0, a) : launch<GemmArgs>(e, k_gemv_ext<__nv_bfloat16, 2>, dim3(gx, groups), dim3(256), 0, a);
         return f32 ? launch<GemmArgs>(e, k_gemv<float>, dim3(gx, groups), dim3(256), 0, a) : launch<GemmArgs>(e, k_gemv<__nv_bfloat16>, dim3(gx, groups), dim3(256), 0, a);
     }
+    if (a.glu) return fail(NB200_EINVAL, "the gated-pair product is a matrix-vector instance (portions of at most %u tokens)", kGemvMaxM);
     const dim3 grid((a.N + 63u) / 64u, (maxM + 63u) / 64u, groups);
     return f32 ? launch<GemmArgs>(e, k_gemm_f32<float>, grid, dim3(256), 0, a) : launch<GemmArgs>(e, k_gemm_bf16, grid, dim3(128), 0, a);
 }
@@ -686,11 +857,96 @@ int mix_window_ssm(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &
     return 0;
 }
 
+// ---- grouped-query differential attention ----
+template <int VCH>
+int diff_attn_launch_v(LayeredEngine *e, const DiffAttnArgs &a, uint32_t qt, uint32_t hpb, size_t smem) {
+    const dim3 grid((a.T + qt - 1) / qt, a.nsplit, (a.H + hpb - 1) / hpb), block(hpb * 32);
+    if (qt == 8) return launch<DiffAttnArgs>(e, k_diff_attn<VCH, 8>, grid, block, smem, a);
+    if (qt == 4) return launch<DiffAttnArgs>(e, k_diff_attn<VCH, 4>, grid, block, smem, a);
+    return launch<DiffAttnArgs>(e, k_diff_attn<VCH, 1>, grid, block, smem, a);
+}
+template <int VCH>
+int diff_attn_optin_v(int smem) {
+    CK(cudaFuncSetAttribute((const void *)k_diff_attn<VCH, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    CK(cudaFuncSetAttribute((const void *)k_diff_attn<VCH, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    CK(cudaFuncSetAttribute((const void *)k_diff_attn<VCH, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    return 0;
+}
+inline int diff_vch(uint32_t vdim) { return vdim <= 32 ? 0 : vdim <= 64 ? 1 : vdim <= 128 ? 2 : 3; }
+
+// one product gives [q | k | v] with their biases; q turns in place, the turned k and v go to the cache pages (this layer's, or none
+// when it reads another layer's); both maps of a head in one warp; output product with its bias
+int mix_diff_attn(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &cx) {
+    const uint32_t E = e->E, T = cx.T, H = L.H, G = L.G, D = L.dim, VD = L.vdim;
+    const bool has_kv = L.kv_from < 0;
+    const uint32_t QW = H * 2 * D, KW = G * 2 * D, P = QW + (has_kv ? KW + G * VD : 0);
+    int r;
+    if ((r = gemm(e, plain(e->hm, E, L.proj, e->b_p, P, T, L.proj_b), 1, T))) return r;
+    if (has_kv || L.rot_tab) {
+        RopeKvArgs ra{e->b_p, P, QW, QW + KW, has_kv ? 1u : 0u, run.cache, cx.table, T, H, G, 2u, D, VD, L.RL, L.rot_dims, cx.pos0, L.rot_tab, cx.pos_ptr};
+        if ((r = launch<RopeKvArgs>(e, k_rope_kv, dim3(T), dim3(256), 0, ra))) return r;
+    }
+    DiffAttnArgs aa{e->b_p, P, run.cache, cx.table, e->b_a, T, H, G, D, VD, L.RL, cx.pos0, L.scale, L.lambda, 1.0f - L.diff, e->eps, cx.pos_ptr, 1u, e->b_dpart, e->b_dtick, L.a_ngk};
+    const bool small = T <= kGemvMaxM;
+    if (cx.pos_ptr) aa.nsplit = kSplitMax;           // the position is not known here: splits without keys write empty partials
+    else if (small) aa.nsplit = std::max(1u, std::min(kSplitMax, (cx.pos0 + T + kPage - 1) / kPage / 2u));
+    const uint32_t qt = small ? 1u : L.a_qt;
+    const size_t smem = diff_attn_smem(D, VD, L.a_ngk, qt, L.a_hpb, diff_attn_vec(D, VD, P));
+    switch (diff_vch(VD)) {
+        case 0: r = diff_attn_launch_v<1>(e, aa, qt, L.a_hpb, smem); break;
+        case 1: r = diff_attn_launch_v<2>(e, aa, qt, L.a_hpb, smem); break;
+        case 2: r = diff_attn_launch_v<4>(e, aa, qt, L.a_hpb, smem); break;
+        default: r = diff_attn_launch_v<8>(e, aa, qt, L.a_hpb, smem);
+    }
+    if (r) return r;
+    return gemm(e, plain(e->b_a, H * VD, L.o, e->d, E, T, L.o_b), 1, T);
+}
+
+// ---- state-space duality (Mamba-2) ----
+// one product gives [z | x | B | C | dt]; [x | B | C] passes its convolution with bias and silu (tail in the slot; for short portions
+// as the product's epilogue); the scan makes dt and the decay itself; gate, group norm and gain; output product
+int mix_ssd(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &cx) {
+    const uint32_t E = e->E, T = cx.T, Hn = L.H, Pd = L.vdim, N = L.mN, G = L.G, inner = Hn * Pd, XW = inner + 2 * G * N, Pw = inner + XW + Hn;
+    int r;
+    const bool small = T <= kGemvMaxM;
+    if (small) {
+        GemmArgs pj = plain(e->hm, E, L.proj, e->b_p, Pw, T, nullptr, EPI_CONV_RANGES);
+        pj.cr[0] = {inner, inner + XW, L.m_conv, L.m_conv_b, cx.st + run.st_conv, e->b_sdx, L.m_taps, 1};
+        if ((r = gemm(e, pj, 1, T))) return r;
+    } else if ((r = gemm(e, plain(e->hm, E, L.proj, e->b_p, Pw, T), 1, T)) ||
+               (r = conv_launch(e, ConvArgs{e->b_p + inner, Pw, L.m_conv, L.m_conv_b, cx.st + run.st_conv, e->b_sdx, T, XW, L.m_taps, XW, 1}))) return r;
+    SsdArgs sa{e->b_sdx, XW, e->b_p + inner + XW, Pw, L.dt_b, L.A, L.Dv, cx.st + run.st_S, e->b_sdy, T, Hn, Pd, N, G, 0u, 0u, e->b_sseg};
+    const uint32_t nseg = T >= 64 ? std::min(kRetSegs, T / 32u) : 1u;
+    if (nseg > 1) sa.seg_len = (T + nseg - 1u) / nseg;
+    // columns per warp: four (fewest staged bytes per FMA) where the grid still gives every SM a dozen warps, else one
+    const uint32_t cpw = (size_t)Hn * Pd / 4u * nseg >= (size_t)e->num_sms * 12u ? 4u : 1u;
+    const dim3 grid((Pd + 8u * cpw - 1u) / (8u * cpw), Hn, nseg), block(256);
+    for (uint32_t pass = (nseg > 1 ? 1u : 0u); pass <= (nseg > 1 ? 2u : 0u); pass++) {
+        sa.mode = pass;
+#define SSD_LAUNCH(DCH) (cpw == 4 ? launch<SsdArgs>(e, k_ssd_scan<DCH, 4>, grid, block, 0, sa) : launch<SsdArgs>(e, k_ssd_scan<DCH, 1>, grid, block, 0, sa))
+        if (N <= 32) r = SSD_LAUNCH(1);
+        else if (N <= 64) r = SSD_LAUNCH(2);
+        else if (N <= 128) r = SSD_LAUNCH(4);
+        else r = SSD_LAUNCH(8);
+#undef SSD_LAUNCH
+        if (r) return r;
+        if (pass == 1) {
+            SsdChainArgs ca{cx.st + run.st_S, e->b_sseg, e->b_p + inner + XW, Pw, L.dt_b, L.A, Hn, Pd, N, T, sa.seg_len, nseg};
+            if ((r = launch<SsdChainArgs>(e, k_ssd_chain, dim3(std::min(8u, (Pd * N + 255u) / 256u), Hn), dim3(256), 0, ca))) return r;
+        }
+    }
+    SsdOutArgs oa{e->b_sdy, e->b_p, Pw, L.gn, e->b_a, T, inner, L.parts, e->eps};
+    if ((r = launch<SsdOutArgs>(e, k_ssd_out, dim3(T * L.parts), dim3(128), 0, oa))) return r;
+    return gemm(e, plain(e->b_a, inner, L.o, e->d, E, T), 1, T);
+}
+
 int mix(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &cx) {
     switch (L.type) {
         case MIX_RGLRU: return mix_rglru(e, L, run, cx);
         case MIX_LATENT_ATTN: return mix_latent_attn(e, L, run, cx);
         case MIX_RETENTION: return mix_retention(e, L, run, cx);
+        case MIX_DIFF_ATTN: return mix_diff_attn(e, L, run, cx);
+        case MIX_SSD: return mix_ssd(e, L, run, cx);
         default: return mix_window_ssm(e, L, run, cx);
     }
 }
@@ -707,6 +963,69 @@ int ff_dense(LayeredEngine *e, const Layer &L, uint32_t T) {
     PolyArgs pa{e->b_f, L.ff, L.act, T, L.ff, e->eps};
     if ((r = launch<PolyArgs>(e, k_polynorm, dim3(T), dim3(256), 0, pa))) return r;
     return gemm(e, plain(e->b_f, L.ff, L.down, e->d, e->E, T), 1, T);
+}
+
+// gated dense feed-forward: e->h2 -> e->d.  Short portions: gate and up rows meet in the matrix-vector kernel; long ones pass k_glu
+int ff_glu_dense(LayeredEngine *e, const Layer &L, uint32_t T) {
+    int r;
+    if (T <= kGemvMaxM) {
+        GemmArgs u = plain(e->h2, e->E, L.up, e->b_f2, L.ff, T);
+        u.N = L.ff; u.glu = 1u;
+        if ((r = gemm(e, u, 1, T))) return r;
+    } else {
+        if ((r = gemm(e, plain(e->h2, e->E, L.up, e->b_f, 2 * L.ff, T), 1, T))) return r;
+        GluArgs ga{e->b_f, 2 * L.ff, e->b_f2, L.ff, nullptr, T, L.ff, 0u};
+        if ((r = launch<GluArgs>(e, k_glu, dim3(ew_grid((size_t)T * L.ff)), dim3(256), 0, ga))) return r;
+    }
+    return gemm(e, plain(e->b_f2, L.ff, L.down, e->d, e->E, T), 1, T);
+}
+
+// experts chosen by sigmoid scores: e->h2 -> the rows of e->b_eo (one per token and choice, in expert order) and, with a shared expert,
+// e->b_so and the gate logits e->b_sg; the residual kernel adds them up.  The score weights the expert's INPUT; the experts have no
+// bias, so act(s g) (s u) of the unweighted products g, u is the same number.  The shared expert runs on a second stream.
+int ff_moe_scored(LayeredEngine *e, const Layer &L, uint32_t T) {
+    const uint32_t E = e->E, NL = L.NE + (L.has_shared ? 1u : 0u);
+    const bool small = T <= kGemvMaxM;
+    int r;
+    if (L.has_shared && e->branch_streams) CK(cudaEventRecord(e->ev_fork, e->stream));
+    RouteArgs ra{e->h2, L.router, e->b_idx, e->b_wt, e->b_cnt, e->b_off, e->b_fill, e->b_slot, e->b_rows, T, L.NE, L.top, E, 1u, L.has_shared ? 1u : 0u, e->b_sg, e->b_wrow};
+    if (small) { if ((r = launch<RouteArgs>(e, k_route_small, dim3(1), dim3(1024), route_smem(NL, 1024), ra))) return r; }
+    else if ((r = launch<RouteArgs>(e, k_route, dim3(T), dim3(256), route_smem(NL, 256), ra)) || (r = launch<RouteArgs>(e, k_route_place, dim3(1), dim3(1024), 0, ra))) return r;
+    GemmArgs u{};
+    u.A = e->h2; u.lda = E; u.W = L.up.p; u.ldw = E; u.M = T; u.K = E; u.a_gmod = 1;
+    u.g_off = e->b_off; u.a_rows = e->b_rows; u.w_gstride = (uint64_t)2 * L.ff * E;
+    if (small) { u.C = e->b_hb; u.ldc = L.ff; u.N = L.ff; u.glu = 2u; u.row_scale = e->b_wrow; }
+    else { u.C = e->b_hg; u.ldc = 2 * L.ff; u.N = 2 * L.ff; }
+    if ((r = gemm(e, u, L.NE, T, false, T * L.top))) return r;
+    if (!small) {
+        GluArgs ga{e->b_hg, 2 * L.ff, e->b_hb, L.ff, e->b_wrow, T * L.top, L.ff, 1u};
+        if ((r = launch<GluArgs>(e, k_glu, dim3(ew_grid((size_t)T * L.top * L.ff)), dim3(256), 0, ga))) return r;
+    }
+    GemmArgs dn{};
+    dn.A = e->b_hb; dn.lda = L.ff; dn.W = L.down.p; dn.ldw = L.ff; dn.C = e->b_eo; dn.ldc = E; dn.M = T; dn.N = E; dn.K = L.ff; dn.a_gmod = 1;
+    dn.g_off = e->b_off; dn.w_gstride = (uint64_t)E * L.ff;
+    if ((r = gemm(e, dn, L.NE, T, false, T * L.top))) return r;
+    if (!L.has_shared) return 0;
+    if (e->branch_streams) { e->cur = e->side; CK(cudaStreamWaitEvent(e->side, e->ev_fork, 0)); }
+    if (small) {
+        GemmArgs su = plain(e->h2, E, L.sup, e->b_sh2, L.sff, T);
+        su.N = L.sff; su.glu = 2u;
+        if ((r = gemm(e, su, 1, T))) return r;
+    } else {
+        if ((r = gemm(e, plain(e->h2, E, L.sup, e->b_sh, 2 * L.sff, T), 1, T))) return r;
+        GluArgs ga{e->b_sh, 2 * L.sff, e->b_sh2, L.sff, nullptr, T, L.sff, 1u};
+        if ((r = launch<GluArgs>(e, k_glu, dim3(ew_grid((size_t)T * L.sff)), dim3(256), 0, ga))) return r;
+    }
+    if ((r = gemm(e, plain(e->b_sh2, L.sff, L.sdown, e->b_so, E, T), 1, T))) return r;
+    if (e->branch_streams) { CK(cudaEventRecord(e->ev_join, e->side)); e->cur = e->stream; CK(cudaStreamWaitEvent(e->stream, e->ev_join, 0)); }
+    return 0;
+}
+
+// x += dyt_post(sublayer output); out = dyt_pre(x) when a sublayer follows.  moe: the output is the experts' rows (+ the gated shared expert)
+int dyt_residual(LayeredEngine *e, const Layer *moe, const Dyt &post, const Dyt *pre, float *out, float *keep, uint32_t T) {
+    DytResArgs a{e->x, moe ? nullptr : e->d, moe ? e->b_eo : nullptr, e->b_slot, moe ? moe->top : 0u, moe && moe->has_shared ? e->b_so : nullptr, e->b_sg,
+                 post, pre ? *pre : Dyt{}, pre ? out : nullptr, keep, T, e->E};
+    return launch<DytResArgs>(e, k_dyt_residual, dim3(ew_grid((size_t)T * e->E)), dim3(256), 0, a);
 }
 
 int sandwich(LayeredEngine *e, const float *d, const float *w_post, const float *w_pre, float *out, float *keep, uint32_t T, const float *d2 = nullptr) {
@@ -727,6 +1046,17 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const
         const Run &run = e->runs[ri];
         const Layer &L = e->layers[run.layer];
         float *keep = e->keep ? e->keep + ri * (size_t)e->chunk_cap * E : nullptr;
+        if (e->form == FORM_SANDWICH && e->norm_kind == NORM_DYT) {
+            // the same two updates through Dynamic-Tanh norms; e->hm already holds norm1(x) (from the embedding or the update before)
+            const Dyt *next_d1 = ri + 1 < e->runs.size() ? &e->layers[e->runs[ri + 1].layer].d1 : nullptr;
+            if ((r = mix(e, L, run, cx))) return r;
+            if (L.has_mlp) {
+                if ((r = dyt_residual(e, nullptr, L.d1b, &L.d2, e->h2, nullptr, T))) return r;
+                const bool moe = L.ff_kind == FF_MOE_SCORED;
+                if ((r = moe ? ff_moe_scored(e, L, T) : ff_glu_dense(e, L, T)) || (r = dyt_residual(e, moe ? &L : nullptr, L.d2b, next_d1, e->hm, keep, T))) return r;
+            } else if ((r = dyt_residual(e, nullptr, L.d1b, next_d1, e->hm, keep, T))) return r;
+            continue;
+        }
         if (e->form == FORM_SANDWICH) {
             // x <- x + norm1b(mixer(norm1 x)), x <- x + norm2b(ff(norm2 x)): each residual update also norms the updated x for the
             // sublayer that follows (this layer's feed-forward, or the next run's mixer)
@@ -779,7 +1109,13 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const
     return 0;
 }
 
-int embed_tokens(LayeredEngine *e, const uint32_t *tok_dev, uint32_t T, const uint32_t *pos_ptr = nullptr, uint32_t pos0 = 0) {
+int embed_tokens(LayeredEngine *e, uint32_t slot, const uint32_t *tok_dev, uint32_t T, const uint32_t *pos_ptr = nullptr, uint32_t pos0 = 0) {
+    if (e->norm_kind == NORM_DYT) {      // token row x scale + pair row, the stack's input norm, and the first sublayer's input norm
+        e->cur = e->stream;
+        EmbedPairArgs a{tok_dev, pos_ptr, e->embed.p, e->pairs.p, e->x, e->hm, reinterpret_cast<uint32_t *>(e->state + (size_t)slot * e->slot_floats + e->st_tok),
+                        T, e->E, e->buckets, e->mul_prev, e->mul_cur, e->emb_scale, e->embed_norm, e->layers[e->runs[0].layer].d1};
+        return e->f32 ? launch<EmbedPairArgs>(e, k_embed_pair<float>, dim3(T), dim3(128), 0, a) : launch<EmbedPairArgs>(e, k_embed_pair<__nv_bfloat16>, dim3(T), dim3(128), 0, a);
+    }
     if (e->max_pos) {      // a learned position row joins the token row
         if (e->f32) k_embed_pos<float><<<T, 128, 0, e->stream>>>(tok_dev, pos_ptr, (const float *)e->embed.p, (const float *)e->pos_table.p, e->x, e->E, pos0);
         else k_embed_pos<__nv_bfloat16><<<T, 128, 0, e->stream>>>(tok_dev, pos_ptr, (const __nv_bfloat16 *)e->embed.p, (const __nv_bfloat16 *)e->pos_table.p, e->x, e->E, pos0);
@@ -796,6 +1132,12 @@ int embed_tokens(LayeredEngine *e, const uint32_t *tok_dev, uint32_t T, const ui
 
 // logits of `nw` rows of the current chunk (want_dev holds their indices) -> e->logits [nw][V]
 int head_rows(LayeredEngine *e, uint32_t nw, const uint32_t *want_dev = nullptr) {
+    if (e->norm_kind == NORM_DYT) {
+        k_final_dyt<<<nw, 256, 0, e->stream>>>(e->x, want_dev ? want_dev : e->want_dev, e->final_dyt, e->b_xn, e->E);
+        CK(cudaGetLastError());
+        e->launches++;
+        return gemm(e, plain(e->b_xn, e->E, e->head, e->logits, e->V, nw), 1, nw);
+    }
     k_final_norm<<<nw, 256, 0, e->stream>>>(e->x, want_dev ? want_dev : e->want_dev, e->final_norm, e->b_xn, e->E, e->eps, e->form == FORM_SANDWICH ? 1u : 0u);
     CK(cudaGetLastError());
     e->launches++;
@@ -807,7 +1149,7 @@ int head_rows(LayeredEngine *e, uint32_t nw, const uint32_t *want_dev = nullptr)
 // replayed (NB200_FLAG_NO_GRAPH: launched directly).  The caller has reserved the page and set *dpos.
 int decode_launches(LayeredEngine *e, uint32_t slot) {
     int r;
-    if ((r = embed_tokens(e, e->ids_dev, 1, e->dpos)) || (r = run_layers(e, slot, 1, 0, e->dpos))) return r;
+    if ((r = embed_tokens(e, slot, e->ids_dev, 1, e->dpos)) || (r = run_layers(e, slot, 1, 0, e->dpos))) return r;
     return head_rows(e, 1, e->zero_dev);
 }
 
@@ -885,7 +1227,7 @@ int step_dev(LayeredEngine *e, uint32_t seq, const uint32_t *tok_dev, uint32_t n
     uint32_t wi = 0;
     for (uint32_t c0 = 0; c0 < n; c0 += e->chunk_cap) {
         const uint32_t T = std::min(e->chunk_cap, n - c0);
-        if ((r = embed_tokens(e, tok_dev + c0, T, nullptr, s.len)) || (r = run_layers(e, seq, T, s.len))) return r;
+        if ((r = embed_tokens(e, seq, tok_dev + c0, T, nullptr, s.len)) || (r = run_layers(e, seq, T, s.len))) return r;
         s.len += T;
         while (wi < n_want && want[wi] < c0 + T) {
             uint32_t idx[kWantBatch], nw = 0;
@@ -1186,10 +1528,47 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
     Loader ld{e, dir};
     int r;
     const nb::Json *arch = cfg.get("architecture");
-    e->form = arch && arch->t == nb::Json::Str && arch->str == "Rakarax" ? FORM_SANDWICH : FORM_PARALLEL_SHIFT;
+    const std::string design = arch && arch->t == nb::Json::Str ? arch->str : "";
+    e->form = design == "Rakarax" || design == "Gokinex" ? FORM_SANDWICH : FORM_PARALLEL_SHIFT;
+    e->norm_kind = design == "Gokinex" ? NORM_DYT : NORM_RMS_ZERO;
     if ((r = ld.stacked({"embed"}, {e->V}, E, &e->embed)) || (r = ld.stacked({"head"}, {e->V}, E, &e->head))) return r;
     e->layers.resize(NL);
-    if (e->form == FORM_SANDWICH) {
+    if (e->norm_kind == NORM_DYT) {
+        // embedding: a fixed scale on the token row and, optionally, a table of hashed (previous, current) pairs with one more row
+        // for the first token of a sequence
+        const nb::Json *emb = cfg.get("embedding");
+        double sc = 1.0;
+        if (emb && emb->t == nb::Json::Obj && emb->present("scale") && !emb->number("scale", &sc)) return fail(NB200_EINVAL, "embedding.scale must be a number");
+        e->emb_scale = (float)sc;
+        if (emb && emb->t == nb::Json::Obj && emb->present("bigram")) {
+            const nb::Json *bg = emb->get("bigram");
+            if (!u32_of(bg, "buckets", &e->buckets) || !u32_of(bg, "mul_prev", &e->mul_prev) || !u32_of(bg, "mul_cur", &e->mul_cur) || !e->buckets)
+                return fail(NB200_EINVAL, "embedding.bigram needs buckets > 0, mul_prev and mul_cur");
+            if ((r = ld.stacked({"bigram"}, {(uint64_t)e->buckets + 1u}, E, &e->pairs))) return r;
+        }
+        if ((r = load_dyt(ld, "embed.norm", E, &e->embed_norm)) || (r = load_dyt(ld, "final.norm", E, &e->final_dyt))) return r;
+        for (uint32_t i = 0; i < NL; i++) {
+            Run q; q.layer = i; e->runs.push_back(q);
+            const nb::Json &lj = layers->arr[i];
+            Layer &L = e->layers[i];
+            const std::string p = "l" + std::to_string(i) + ".";
+            const nb::Json *type = lj.get("type"), *mixer = lj.get("mixer");
+            if (!type || type->t != nb::Json::Str || !mixer || mixer->t != nb::Json::Obj) return fail(NB200_EINVAL, "layer %u needs \"type\" and \"mixer\"", i);
+            if ((r = load_dyt(ld, p + "norm1", E, &L.d1)) || (r = load_dyt(ld, p + "norm1b", E, &L.d1b))) return r;
+            if (type->str == "attention") { L.type = MIX_DIFF_ATTN; r = load_diff_attn(ld, mixer, p + "mix.", &L, E, max_tokens, e->layers, i); }
+            else if (type->str == "mamba2") { L.type = MIX_SSD; r = load_ssd(ld, mixer, p + "mix.", &L, E); }
+            else return fail(NB200_EINVAL, "layer %u: mixer type \"%s\" is not known", i, type->str.c_str());
+            if (r) return r;
+            if (lj.present("mlp")) {
+                const nb::Json *f = lj.get("mlp"), *kind = f->get("kind");
+                if ((r = load_dyt(ld, p + "norm2", E, &L.d2)) || (r = load_dyt(ld, p + "norm2b", E, &L.d2b))) return r;
+                if (kind && kind->t == nb::Json::Str && kind->str == "dense") r = load_glu_dense(ld, f, p + "mlp.", &L, E);
+                else if (kind && kind->t == nb::Json::Str && kind->str == "moe") r = load_moe_scored(ld, f, p + "mlp.", &L, E);
+                else return fail(NB200_EINVAL, "layer %u: feed-forward kind \"%s\" is not known", i, kind && kind->t == nb::Json::Str ? kind->str.c_str() : "?");
+                if (r) return r;
+            }
+        }
+    } else if (e->form == FORM_SANDWICH) {
         auto pt = dir->tensors.find("pos");
         if (pt == dir->tensors.end() || pt->second.shape.size() != 2 || pt->second.shape[0] == 0) return fail(NB200_EINVAL, "model.safetensors has no position table \"pos\" [positions, width]");
         e->max_pos = (uint32_t)pt->second.shape[0];
@@ -1257,10 +1636,20 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
     e->chunk_cap = std::max(1u, std::min(max_tokens, env_u32("NB200_CHUNK", 1024)));
     e->n_pages = (max_tokens + kPage - 1) / kPage + e->max_seqs;
     size_t off = 0;
+    if (e->buckets) { e->st_tok = off; off += 4; }      // the sequence's last token + 1, one word (the pair table's hash needs it)
     for (Run &q : e->runs) {
         const Layer &L = e->layers[q.layer];
         if (e->form == FORM_PARALLEL_SHIFT) { q.st_prev = off; off += E; }
         switch (L.type) {
+            case MIX_DIFF_ATTN:      // rows of [rotated keys of both maps | values]; a layer that reads another layer's rows has none
+                if (L.kv_from >= 0) { q.cache = e->runs[L.kv_from].cache; break; }
+                DM(q.cache, (size_t)e->n_pages * kPage * L.RL * 4);
+                CK(cudaMemset(q.cache, 0, (size_t)e->n_pages * kPage * L.RL * 4));
+                break;
+            case MIX_SSD:            // the convolution's tail over [x | B | C] and the state [head][value column][state coordinate]
+                q.st_conv = off; off += (size_t)(L.m_taps - 1) * (L.H * L.vdim + 2 * L.G * L.mN);
+                q.st_S = off; off += (size_t)L.H * L.vdim * L.mN;
+                break;
             case MIX_RGLRU: q.st_S = off; off += L.C; q.st_conv = off; off += (size_t)(L.taps - 1) * L.C; break;
             case MIX_LATENT_ATTN: DM(q.cache, (size_t)e->n_pages * kPage * L.R * 4); break;
             case MIX_RETENTION: q.st_S = off; off += (size_t)L.H * L.vdim * L.dim; break;
@@ -1284,6 +1673,7 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
     const size_t T = e->chunk_cap;
     uint32_t mC = 0, mZ = 0, mQR = 0, mQ = 0, mHR = 0, mOV = 0, mNE = 0, mTop = 0, mFF = 0, mSFF = 0;
     uint32_t sP = 0, sQK = 0, sXC = 0, sA = 0, sRO = 0, sDBC = 0, sF = 0;
+    uint32_t sDP = 0, sDT = 0, sXC2 = 0, sY = 0, sF2 = 0; size_t sSS = 0, diff_smem[4] = {0, 0, 0, 0};      // differential attention, state-space duality, gated feed-forward
     size_t win_smem[4] = {0, 0, 0, 0};      // most shared memory any layer asks of the window-attention instances, per value-column count
     for (const Run &q : e->runs) {
         const Layer &L = e->layers[q.layer];
@@ -1297,7 +1687,33 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
             sm = std::max(sm, std::max(win_attn_smem(L.H, L.dim, L.RL, qt), win_attn_smem(L.H, L.dim, L.RL, 1)));
         }
         if (L.ff_kind == FF_DENSE_POLY) sF = std::max(sF, L.ff);
+        if (L.type == MIX_DIFF_ATTN) {
+            sP = std::max(sP, L.H * 2 * L.dim + (L.kv_from < 0 ? L.G * (2 * L.dim + L.vdim) : 0u)); sA = std::max(sA, L.H * L.vdim);
+            sDP = std::max(sDP, L.H * 2 * (L.vdim + 2)); sDT = std::max(sDT, (L.H + L.a_hpb - 1) / L.a_hpb);
+            const bool vec = diff_attn_vec(L.dim, L.vdim, L.H * 2 * L.dim + (L.kv_from < 0 ? L.G * (2 * L.dim + L.vdim) : 0u));
+            size_t &sm = diff_smem[diff_vch(L.vdim)];
+            sm = std::max(sm, std::max(diff_attn_smem(L.dim, L.vdim, L.a_ngk, L.a_qt, L.a_hpb, vec), diff_attn_smem(L.dim, L.vdim, L.a_ngk, 1, L.a_hpb, vec)));
+        }
+        if (L.type == MIX_SSD) {
+            const uint32_t inner = L.H * L.vdim, XW = inner + 2 * L.G * L.mN;
+            sP = std::max(sP, inner + XW + L.H); sXC2 = std::max(sXC2, XW); sY = std::max(sY, inner); sA = std::max(sA, inner);
+            sSS = std::max(sSS, (size_t)inner * L.mN);
+        }
+        if (L.ff_kind == FF_DENSE_GLU) { sF = std::max(sF, 2 * L.ff); sF2 = std::max(sF2, L.ff); }
     }
+    if (diff_smem[0] > 48 * 1024 && (r = diff_attn_optin_v<1>((int)diff_smem[0]))) return r;
+    if (diff_smem[1] > 48 * 1024 && (r = diff_attn_optin_v<2>((int)diff_smem[1]))) return r;
+    if (diff_smem[2] > 48 * 1024 && (r = diff_attn_optin_v<4>((int)diff_smem[2]))) return r;
+    if (diff_smem[3] > 48 * 1024 && (r = diff_attn_optin_v<8>((int)diff_smem[3]))) return r;
+    if (sDP) {
+        DM(e->b_dpart, (size_t)kGemvMaxM * kSplitMax * sDP * 4);
+        DM(e->b_dtick, (size_t)kGemvMaxM * sDT * 4);
+        CK(cudaMemset(e->b_dtick, 0, (size_t)kGemvMaxM * sDT * 4));
+    }
+    if (sSS) DM(e->b_sseg, (size_t)kRetSegs * sSS * 4);
+    if (sXC2) DM(e->b_sdx, T * sXC2 * 4);
+    if (sY) DM(e->b_sdy, T * sY * 4);
+    if (sF2) DM(e->b_f2, T * sF2 * 4);
     if (sQK && ((r = sel_scan_optin<1>()) || (r = sel_scan_optin<2>()) || (r = sel_scan_optin<4>()) || (r = sel_scan_optin<8>()) || (r = sel_scan_optin<16>()) || (r = sel_scan_optin<32>()))) return r;
     if (win_smem[0] > 48 * 1024 && (r = win_attn_optin_v<1>((int)win_smem[0]))) return r;
     if (win_smem[1] > 48 * 1024 && (r = win_attn_optin_v<2>((int)win_smem[1]))) return r;
@@ -1323,11 +1739,12 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
     if (sA) DM(e->b_a, T * sA * 4);
     if (sRO) DM(e->b_ro, T * sRO * 4);
     if (sF) DM(e->b_f, T * sF * 4);
+    uint32_t mFF2 = 0, mSFF2 = 0;      // scored experts: [gate | up] rows of a prefill portion
     for (const Layer &L : e->layers) {
-        if (L.type == MIX_RETENTION || L.type == MIX_WINDOW_SSM) continue;
         if (L.type == MIX_RGLRU) mC = std::max(mC, L.C);
-        else { mZ = std::max(mZ, L.QR + L.R); mQR = std::max(mQR, L.QR); mQ = std::max(mQ, L.H * L.dim); mHR = std::max(mHR, L.H * L.R); mOV = std::max(mOV, L.H * L.vdim); }
-        if (L.ff_kind == FF_MOE) { mNE = std::max(mNE, L.NE); mTop = std::max(mTop, L.top); mFF = std::max(mFF, L.top * L.ff); mSFF = std::max(mSFF, L.sff); }
+        else if (L.type == MIX_LATENT_ATTN) { mZ = std::max(mZ, L.QR + L.R); mQR = std::max(mQR, L.QR); mQ = std::max(mQ, L.H * L.dim); mHR = std::max(mHR, L.H * L.R); mOV = std::max(mOV, L.H * L.vdim); }
+        if (L.ff_kind == FF_MOE || L.ff_kind == FF_MOE_SCORED) { mNE = std::max(mNE, L.NE + 1u); mTop = std::max(mTop, L.top); mFF = std::max(mFF, L.top * L.ff); mSFF = std::max(mSFF, L.sff); }
+        if (L.ff_kind == FF_MOE_SCORED) { mFF2 = std::max(mFF2, 2 * L.top * L.ff); mSFF2 = std::max(mSFF2, 2 * L.sff); }
     }
     DM(e->x, T * E * 4); DM(e->hm, T * E * 4); DM(e->h2, T * E * 4); DM(e->d, T * E * 4);
     if (e->keep_x0) DM(e->x0, T * E * 4);
@@ -1350,7 +1767,9 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
         DM(e->b_cnt, (size_t)mNE * 4); DM(e->b_off, ((size_t)mNE + 1) * 4); DM(e->b_fill, (size_t)mNE * 4);
         CK(cudaMemset(e->b_cnt, 0, (size_t)mNE * 4));
         DM(e->b_hb, T * mFF * 4); DM(e->b_eo, T * mTop * E * 4);
-        if (mSFF) { DM(e->b_sh, T * mSFF * 4); DM(e->b_so, T * E * 4); }
+        if (mSFF) { DM(e->b_sh, T * std::max(mSFF, mSFF2) * 4); DM(e->b_so, T * E * 4); }
+        if (mFF2) { DM(e->b_hg, T * mFF2 * 4); DM(e->b_wrow, T * mTop * 4); DM(e->b_sg, T * 4); }
+        if (mSFF2) DM(e->b_sh2, T * mSFF * 4);
     }
     DM(e->dpos, 64); DM(e->zero_dev, 64);
     CK(cudaMemset(e->dpos, 0, 64)); CK(cudaMemset(e->zero_dev, 0, 64));

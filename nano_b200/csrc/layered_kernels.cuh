@@ -69,6 +69,10 @@ struct GemmArgs {
     // k_gemv only.  Epilogue EPI_CONV_RANGES: a column n inside [cr[i].n0, cr[i].n1) is channel n - n0 of causal convolution i over the
     // rows in order (no epilogue before it); every other column is stored as usual.
     struct ConvRange { uint32_t n0, n1; const float *taps, *bias; float *state, *out; uint32_t K, act; } cr[2];
+    // k_gemv only.  Gated pair (glu 1: gelu_tanh, 2: silu): W holds 2 N rows per group, [gate rows | up rows]; column n of C receives
+    // act(s g_n) (s u_n) with g_n, u_n the products of rows n and N + n and s = row_scale[row] (1 when null): a routed expert whose
+    // input is weighted by the router's score, without a pass over the input.
+    uint32_t glu; const float *row_scale;
 };
 
 // Programmatic dependent launch: every kernel first lets the NEXT kernel of its stream be scheduled (its blocks then sit in their own
@@ -394,7 +398,8 @@ __device__ __forceinline__ void warp_dots(const WT *wr, const float *(&ap)[kGemv
         for (int o = 16; o > 0; o >>= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
 }
 
-// EXT 1: the instance that also knows the convolution-range epilogue, EXT 2: the PolyNorm prologue (registers the plain one keeps)
+// EXT 1: the instance that also knows the convolution-range epilogue, EXT 2: the PolyNorm prologue, EXT 3: the gated pair (registers
+// the plain one keeps)
 template <typename WT, int EXT = 0>
 __device__ __forceinline__ void gemv_body(const GemmArgs &a, float *red) {
     const GroupView gv = group_view(a, blockIdx.y);
@@ -447,6 +452,18 @@ __device__ __forceinline__ void gemv_body(const GemmArgs &a, float *red) {
     for (uint32_t n = warp0; n < a.N; n += nwarps) {
         float acc[kGemvMaxM];
         warp_dots<WT, EXT == 2>(W + (size_t)n * a.ldw, ap, rows, a.K, kvec, sc, a.a_norm_w, a.round_a != 0, lane, acc, (EXT == 2 && a.a_poly) ? pc : nullptr);
+        if (EXT == 3) {          // the up row of the pair, then act(s g) (s u)
+            float up[kGemvMaxM];
+            warp_dots<WT, false>(W + (size_t)(a.N + n) * a.ldw, ap, rows, a.K, kvec, sc, nullptr, a.round_a != 0, lane, up);
+            if (lane != 0) continue;
+#pragma unroll
+            for (uint32_t i = 0; i < kGemvMaxM; i++)
+                if (i < rows) {
+                    const float s = a.row_scale ? a.row_scale[gv.r0 + i] : 1.0f, g = acc[i] * s, u = up[i] * s;
+                    store_c(a, a.C + (size_t)(gv.r0 + i) * a.ldc + gv.c0 + n, (a.glu == 2u ? g / (1.0f + expf(-g)) : gelu_tanh(g)) * u);
+                }
+            continue;
+        }
         if (lane != 0) continue;
         if (EXT == 1 && a.epi == EPI_CONV_RANGES) {
             bool done = false;
@@ -950,18 +967,24 @@ __global__ void __launch_bounds__(kAttnWarps * 32, attn_two_blocks(RCH, QT, EXAC
 // One block per token: router logits z_e = W_router[e] . h in fp32 (a warp per expert, lanes stride over the width), then the
 // `top` largest (ties: the lower expert index first) and their weights = softmax over the chosen logits only; counts[e] += 1 per
 // choice.  Dynamic shared memory: route_smem(NE, threads) bytes.
-struct RouteArgs { const float *h; const float *router; uint32_t *idx; float *wt; uint32_t *counts; uint32_t *off; uint32_t *fill; uint32_t *slot; uint32_t *rows; uint32_t T, NE, top, E; };
-// dynamic shared memory of k_route / k_route_small launched with `threads` threads
+// mode 0: weights = softmax over the chosen logits; mode 1: weights = sigmoid of the chosen logits, as they are (not renormalised).
+// extra: the router matrix carries that many more rows after the experts'; their logits go to extra_out [T][extra] and take no part
+// in the choice (a gate of a shared expert, computed with the router's precision).  wrow (optional): the weights once more in
+// expert-sorted row order, wrow[slot[t][j]] = wt[t][j], for a product that scales its rows.
+struct RouteArgs { const float *h; const float *router; uint32_t *idx; float *wt; uint32_t *counts; uint32_t *off; uint32_t *fill; uint32_t *slot; uint32_t *rows; uint32_t T, NE, top, E;
+                   uint32_t mode, extra; float *extra_out; float *wrow; };
+// dynamic shared memory of k_route / k_route_small launched with `threads` threads (NE: rows of the router matrix, extra ones included)
 inline size_t route_smem(uint32_t NE, uint32_t threads) { const uint32_t nw = threads / 32u; return ((size_t)NE + (size_t)NE * (nw > NE ? nw / NE : 1u)) * 4; }
 // router logits of token t into z[NE].  The blockDim/32 warps are dealt out as `ns` slices per expert (ns = warps / NE, at least 1):
 // a warp sums its slice of the row, the slices are added in order.  zp: NE * ns floats of scratch.
 __device__ __forceinline__ uint32_t route_slices(uint32_t NE) { const uint32_t nw = blockDim.x >> 5; return nw > NE ? nw / NE : 1u; }
 __device__ __forceinline__ void route_logits(const RouteArgs &a, uint32_t t, float *z, float *zp) {
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, nw = blockDim.x >> 5, ns = route_slices(a.NE);
+    const uint32_t NL = a.NE + a.extra;          // rows of the router matrix
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, nw = blockDim.x >> 5, ns = route_slices(NL);
     const float *h = a.h + (size_t)t * a.E;
     const bool vec = (a.E % 4u) == 0;
     const uint32_t per = ((a.E + ns - 1u) / ns + 3u) & ~3u;          // slice length, a multiple of 4
-    for (uint32_t job = warp; job < a.NE * ns; job += nw) {
+    for (uint32_t job = warp; job < NL * ns; job += nw) {
         const uint32_t e = job / ns, sl = job % ns;
         const uint32_t k0 = min(a.E, sl * per), k1 = min(a.E, k0 + per);
         const float *w = a.router + (size_t)e * a.E;
@@ -979,7 +1002,7 @@ __device__ __forceinline__ void route_logits(const RouteArgs &a, uint32_t t, flo
         if (lane == 0) zp[job] = acc;
     }
     __syncthreads();
-    for (uint32_t e = threadIdx.x; e < a.NE; e += blockDim.x) {
+    for (uint32_t e = threadIdx.x; e < NL; e += blockDim.x) {
         float v = 0.0f;
         for (uint32_t sl = 0; sl < ns; sl++) v += zp[e * ns + sl];
         z[e] = v;
@@ -997,6 +1020,8 @@ __device__ __forceinline__ void route_pick(const RouteArgs &a, uint32_t t, float
         idx[j] = bi; wt[j] = best;
         z[bi] = -INFINITY;                 // taken (a logit that IS -inf can only tie with taken ones after all finite ones are gone)
     }
+    for (uint32_t k = 0; k < a.extra; k++) a.extra_out[(size_t)t * a.extra + k] = z[a.NE + k];
+    if (a.mode == 1u) { for (uint32_t j = 0; j < a.top; j++) wt[j] = sigmoidf_(wt[j]); return; }
     const float mx = wt[0];
     float s = 0.0f;
     for (uint32_t j = 0; j < a.top; j++) { wt[j] = expf(wt[j] - mx); s += wt[j]; }
@@ -1005,7 +1030,7 @@ __device__ __forceinline__ void route_pick(const RouteArgs &a, uint32_t t, float
 __global__ void __launch_bounds__(256) k_route(const RouteArgs a) {
     pdl_enter();
     extern __shared__ float z[];
-    route_logits(a, blockIdx.x, z, z + a.NE);
+    route_logits(a, blockIdx.x, z, z + a.NE + a.extra);
     __syncthreads();
     if (threadIdx.x) return;
     route_pick(a, blockIdx.x, z);
@@ -1018,7 +1043,7 @@ __global__ void __launch_bounds__(1024) k_route_small(const RouteArgs a) {
     extern __shared__ float z[];
     uint32_t *cur = reinterpret_cast<uint32_t *>(z);          // after the last token z is free
     for (uint32_t t = 0; t < a.T; t++) {
-        route_logits(a, t, z, z + a.NE);
+        route_logits(a, t, z, z + a.NE + a.extra);
         __syncthreads();
         if (threadIdx.x == 0) route_pick(a, t, z);
         __syncthreads();
@@ -1030,7 +1055,7 @@ __global__ void __launch_bounds__(1024) k_route_small(const RouteArgs a) {
     uint32_t s = 0;
     for (uint32_t e = 0; e < a.NE; e++) { const uint32_t c = cur[e]; a.off[e] = s; cur[e] = s; s += c; }
     a.off[a.NE] = s;
-    for (uint32_t i = 0; i < n; i++) { const uint32_t sl = cur[a.idx[i]]++; a.slot[i] = sl; a.rows[sl] = i / a.top; }
+    for (uint32_t i = 0; i < n; i++) { const uint32_t sl = cur[a.idx[i]]++; a.slot[i] = sl; a.rows[sl] = i / a.top; if (a.wrow) a.wrow[sl] = a.wt[i]; }
 }
 // One block: off[e] = rows before expert e (off[NE] = total), counters cleared for the next use; then slot[t][j] = the row of
 // (token t, choice j) in the expert-sorted order and rows[slot] = t
@@ -1046,6 +1071,7 @@ __global__ void __launch_bounds__(1024) k_route_place(const RouteArgs a) {
         const uint32_t e = a.idx[i];
         const uint32_t s = a.off[e] + atomicAdd(a.fill + e, 1u);
         a.slot[i] = s; a.rows[s] = i / a.top;
+        if (a.wrow) a.wrow[s] = a.wt[i];
     }
 }
 

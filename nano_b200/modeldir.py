@@ -1,4 +1,4 @@
-"""Model folders (config.json + model.safetensors) from the Python side: a writer, and random-weight Famudra and Rakarax models for
+"""Model folders (config.json + model.safetensors) from the Python side: a writer, and random-weight Famudra, Rakarax and Gokinex models for
 the benchmarks and tests.  The reader the engine uses is native (csrc/modeldir.cu); nothing here is on the compute path.
 
 A safetensors file is an 8-byte little-endian header length, that many bytes of JSON (name -> dtype, shape, data_offsets) and
@@ -179,4 +179,77 @@ def rakarax_random(config: dict, seed: int = 0, gain: float = 1.0) -> Dict[str, 
                 t[p + n] = vecn(E, -0.2, 0.2)
             t[p + "mlp.up"] = lin(f["ff"], E, 1.5); t[p + "mlp.down"] = lin(E, f["ff"])
             t[p + "mlp.act"] = bf16_round(np.array([0.6, 0.3, 0.15, 0.05], np.float32) * rng.uniform(0.7, 1.3, size=4).astype(np.float32))
+    return t
+
+
+def gokinex_config(vocab: int, width: int, layers, scale: float = 1.0, bigram=None, eps: float = 1e-5) -> dict:
+    """layers: list of (type, mixer, mlp).
+    type "attention": mixer {heads, kv_heads, dim, vdim, scale, diff, rot: {dims, base, scaling: {factor, low, high, original} or
+    absent} or absent, kv_from: j or absent}; type "mamba2": mixer {heads, vdim, state, groups, conv, norm_groups};
+    mlp: None, {"kind": "dense", "ff": f} or {"kind": "moe", "router": {"experts": n, "top": k}, "expert": {"ff": f}, "shared": {"ff": s}
+    (optional)}.  bigram: {"buckets": b, "mul_prev": p, "mul_cur": c} or None."""
+    out = [{"type": kind, "mixer": json.loads(json.dumps(mixer)), "mlp": json.loads(json.dumps(mlp)) if mlp else None} for kind, mixer, mlp in layers]
+    emb = {"scale": scale}
+    if bigram:
+        emb["bigram"] = dict(bigram)
+    return {"architecture": "Gokinex", "vocab": vocab, "width": width, "embedding": emb, "norm": {"eps": eps}, "layers": out}
+
+
+def gokinex_random(config: dict, seed: int = 0, gain: float = 1.0) -> Dict[str, np.ndarray]:
+    """Random weights (bfloat16-representable fp32 arrays) for a Gokinex config: projections ~ N(0, gain^2 / fan_in)."""
+    rng = np.random.default_rng(seed)
+    E, V = config["width"], config["vocab"]
+
+    def lin(o, i, g=1.0):
+        return bf16_round((rng.standard_normal((o, i), dtype=np.float32) * (gain * g / np.sqrt(i))).astype(np.float32))
+
+    def vecn(n, lo, hi):
+        return bf16_round(rng.uniform(lo, hi, size=n).astype(np.float32))
+
+    t = {}
+
+    def dyt(name, alpha=(0.3, 0.9)):
+        t[name] = vecn(E, 0.6, 1.4); t[name + ".b"] = vecn(E, -0.2, 0.2); t[name + ".alpha"] = vecn((), *alpha)
+
+    t["embed"] = bf16_round(rng.standard_normal((V, E), dtype=np.float32))
+    bg = config["embedding"].get("bigram")
+    if bg:
+        t["bigram"] = bf16_round(rng.standard_normal((bg["buckets"] + 1, E), dtype=np.float32))
+    dyt("embed.norm", (0.2, 0.6)); dyt("final.norm")
+    t["head"] = lin(V, E)
+    for i, L in enumerate(config["layers"]):
+        p = f"l{i}."
+        dyt(p + "norm1"); dyt(p + "norm1b", (0.5, 1.5))
+        m = L["mixer"]
+        if L["type"] == "attention":
+            H, G, D, VD = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            t[p + "mix.q"] = lin(H * 2 * D, E, 2.0); t[p + "mix.q.b"] = vecn(H * 2 * D, -0.3, 0.3)
+            if "kv_from" not in m:
+                t[p + "mix.k"] = lin(G * 2 * D, E, 2.0); t[p + "mix.k.b"] = vecn(G * 2 * D, -0.3, 0.3)
+                t[p + "mix.v"] = lin(G * VD, E); t[p + "mix.v.b"] = vecn(G * VD, -0.3, 0.3)
+            for n in ("lq1", "lk1", "lq2", "lk2"):
+                t[p + "mix." + n] = bf16_round((rng.standard_normal(D) * 0.35 / np.sqrt(np.sqrt(D))).astype(np.float32))
+            t[p + "mix.o"] = lin(E, H * VD); t[p + "mix.o.b"] = vecn(E, -0.2, 0.2)
+        else:
+            Hn, P, N, G, K = m["heads"], m["vdim"], m["state"], m["groups"], m["conv"]
+            inner, XW = Hn * P, Hn * P + 2 * G * N
+            t[p + "mix.in"] = lin(2 * inner + 2 * G * N + Hn, E)
+            t[p + "mix.conv"] = vecn((XW, K), -0.6, 0.6); t[p + "mix.conv.b"] = vecn(XW, -0.1, 0.1)
+            t[p + "mix.dt_bias"] = vecn(Hn, -4.0, 0.5); t[p + "mix.A_log"] = bf16_round(np.log(rng.uniform(0.05, 8.0, size=Hn)).astype(np.float32))
+            t[p + "mix.D"] = vecn(Hn, 0.5, 1.5); t[p + "mix.norm"] = vecn(inner, 0.6, 1.4); t[p + "mix.o"] = lin(E, inner)
+        f = L.get("mlp")
+        if not f:
+            continue
+        dyt(p + "norm2"); dyt(p + "norm2b", (0.5, 1.5))
+        if f["kind"] == "dense":
+            t[p + "mlp.gate"] = lin(f["ff"], E, 1.5); t[p + "mlp.up"] = lin(f["ff"], E); t[p + "mlp.down"] = lin(E, f["ff"])
+        else:
+            t[p + "mlp.router"] = lin(f["router"]["experts"], E, 2.0)
+            for e in range(f["router"]["experts"]):
+                q = p + f"mlp.e{e}."
+                t[q + "gate"] = lin(f["expert"]["ff"], E, 1.5); t[q + "up"] = lin(f["expert"]["ff"], E); t[q + "down"] = lin(E, f["expert"]["ff"])
+            if f.get("shared"):
+                q = p + "mlp.shared."
+                t[q + "gate"] = lin(f["shared"]["ff"], E, 1.5); t[q + "up"] = lin(f["shared"]["ff"], E); t[q + "down"] = lin(E, f["shared"]["ff"])
+                t[q + "sg"] = lin(1, E, 2.0)
     return t
