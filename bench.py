@@ -674,6 +674,98 @@ def rakarax_bench(args):
                       "clocks": clocks, "sizes": out}))
 
 
+# --------------------------------------------------------------------------------------------------
+# --design gokinex: the same two measurements for the Gokinex design (Mamba-2 scan and grouped-query differential attention layers,
+# gated dense and score-weighted expert feed-forwards, Dynamic-Tanh norms) beside the closest model of the same runtime, Rakarax
+# (the other sequential-sublayer design: grouped-query window attention + selective scan, retention, dense feed-forward), at equal
+# width and depth.
+# --------------------------------------------------------------------------------------------------
+GOKINEX_SIZES = {
+    # name: (width, layers, attention heads, kv heads, dim per map, vdim, scan heads, scan vdim, scan state, dense ff, experts, top, expert ff, shared ff)
+    "w1024": (1024, 8, 16, 4, 64, 64, 32, 64, 128, 3072, 16, 2, 512, 1024),
+    "w2048": (2048, 8, 16, 4, 64, 128, 64, 64, 128, 6144, 16, 2, 1024, 2048),
+}
+
+
+def gokinex_model(name):
+    from nano_b200 import modeldir as md
+    E_, L, H, G, D, VD, SH, SP, SN, ff, NE, top, eff, sff = GOKINEX_SIZES[name]
+    rot = {"dims": D, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    ssd = {"heads": SH, "vdim": SP, "state": SN, "groups": 1, "conv": 4, "norm_groups": 1}
+    moe = {"kind": "moe", "router": {"experts": NE, "top": top}, "expert": {"ff": eff}, "shared": {"ff": sff}}
+    layers = []
+    for i in range(L):
+        if i % 2 == 0:
+            layers.append(("mamba2", ssd, {"kind": "dense", "ff": ff}))
+        else:
+            att = {"heads": H, "kv_heads": G, "dim": D, "vdim": VD, "scale": D ** -0.5, "diff": 0.5, "rot": rot}
+            if i % 4 == 3:
+                att["kv_from"] = i - 2          # every second attention layer reads the keys and values of the one before
+            layers.append(("attention", att, moe))
+    cfg = md.gokinex_config(FAMUDRA_VOCAB, E_, layers, scale=float(E_) ** 0.5, bigram={"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31})
+    path = os.path.join(os.environ.get("NB200_MODEL_CACHE", "/tmp/nb200_models"), f"gokinex-{name}")
+    if not os.path.exists(os.path.join(path, "model.safetensors")):
+        md.write_model_dir(path + ".part", cfg, md.gokinex_random(cfg, 0))
+        os.replace(path + ".part", path)
+    return path, cfg
+
+
+def gokinex_decode_bytes(cfg, pos, wbytes=2):
+    """Algorithmic HBM bytes of one decoded token at position pos: every matrix once (the chosen experts only), the fp32 scan states
+    read and written, the fp32 key/value rows of every attention layer (a layer that shares another's rows reads them again), the head."""
+    E_ = cfg["width"]; b = 0.0
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        if L["type"] == "attention":
+            H, G, D, VD = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            own = 0 if "kv_from" in m else G * (2 * D + VD)
+            b += wbytes * ((2 * H * D + own) * E_ + E_ * H * VD) + 4.0 * G * (2 * D + VD) * (pos + 1)
+        else:
+            Hn, P, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
+            b += wbytes * ((2 * Hn * P + 2 * G * N + Hn) * E_ + E_ * Hn * P) + 8.0 * Hn * P * N
+        f = L.get("mlp")
+        if f and f["kind"] == "dense":
+            b += wbytes * 3 * E_ * f["ff"]
+        elif f:
+            b += 4.0 * (f["router"]["experts"] + 1) * E_ + wbytes * 3 * E_ * (f["router"]["top"] * f["expert"]["ff"] + (f["shared"]["ff"] if f.get("shared") else 0))
+    return b + wbytes * cfg["vocab"] * E_
+
+
+def gokinex_flops_per_token(cfg, ctx):
+    fl = 2.0 * (gokinex_decode_bytes(cfg, 0, 1) - cfg["vocab"] * cfg["width"])
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        if L["type"] == "attention":
+            fl += 4.0 * m["heads"] * (m["dim"] + m["vdim"]) * ctx          # two maps: scores over dim each, weighted sums over vdim each
+        else:
+            fl += 6.0 * m["heads"] * m["vdim"] * m["state"]
+    return fl
+
+
+def gokinex_bench(args):
+    from nano_b200 import engine as E
+    hbm, hbm_src = peaks()
+    try:
+        tf = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        tf = 1590.0
+    ctx, n_dec, T = 1024, 128, 2048
+    sampler = ClockSampler(0); sampler.start()
+    out = {}
+    for name in (args.sizes.split(",") if args.sizes else sorted(GOKINEX_SIZES)):
+        path, cfg = gokinex_model(name)
+        row = layered_modes(E, path, FAMUDRA_VOCAB, ctx, n_dec, T, args, hbm, tf, lambda pos, wb: gokinex_decode_bytes(cfg, pos, wb), lambda c: gokinex_flops_per_token(cfg, c))
+        ppath, pcfg = rakarax_model(name)          # the closest model: the same runtime's Rakarax at equal width and depth
+        args_bf16 = argparse.Namespace(**{**vars(args), "with_f32": False})
+        row["peer_rakarax"] = layered_modes(E, ppath, FAMUDRA_VOCAB, ctx, n_dec, T, args_bf16, hbm, tf, lambda pos, wb: rakarax_decode_bytes(pcfg, pos, wb), lambda c: rakarax_flops_per_token(pcfg, c))["bf16"]
+        out[name] = row
+    clocks = sampler.stop()
+    print(json.dumps({"design": "gokinex", "unit": "tokens/s", "n_gpus": 1, "data": "synthetic (random weights)", "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "bf16_tflops": tf},
+                      "config": {"decode": f"greedy device loop, {n_dec} tokens after a {ctx}-token prompt, batch 1", "prefill": f"one portion of {T} tokens into an empty sequence",
+                                 "timing": "CUDA events on the engine's stream after warm-up", "l2": "fractions are against HBM although the weights of one token fit the 126 MB L2 at w1024"},
+                      "clocks": clocks, "sizes": out}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -690,7 +782,7 @@ def main():
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-stream", action="store_true", help="forbid the streaming kernel")
-    ap.add_argument("--design", default=None, choices=["famudra", "rakarax"], help="measure a model-folder design instead of the headline workload (its own JSON line)")
+    ap.add_argument("--design", default=None, choices=["famudra", "rakarax", "gokinex"], help="measure a model-folder design instead of the headline workload (its own JSON line)")
     ap.add_argument("--sizes", default=None, help="--design: comma-separated size names (default: all)")
     ap.add_argument("--with-f32", action="store_true", help="--design: also time the true-32-bit mode")
     args = ap.parse_args()
@@ -699,6 +791,9 @@ def main():
         return
     if args.design == "rakarax":
         rakarax_bench(args)
+        return
+    if args.design == "gokinex":
+        gokinex_bench(args)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
