@@ -93,6 +93,7 @@ struct Layer {
     // scale, rot_dims, rot_tab, RL as above; lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff
     int kv_from = -1; float diff = 0.0f, lambda = 0.0f; float *proj_b = nullptr, *o_b = nullptr;
     uint32_t a_hpb = 0, a_ngk = 0, a_qt = 0;      // heads per attention block, kv heads such a block stages, query tokens per prefill block
+    uint32_t a_hpb1 = 0, a_ngk1 = 0;              // the same for short portions: blocks of one kv head's query heads, so that more blocks share the keys
     // state-space duality: proj = [z | x | B | C | dt]; H heads of vdim, mN states, G groups, m_taps, m_conv, m_conv_b, dt_b, A = exp(A_log)
     // per head, Dv per head; the output is normed in `parts` equal parts with the gain gn
     uint32_t parts = 0; float *gn = nullptr;
@@ -407,6 +408,8 @@ int load_dense(Loader &ld, const nb::Json *f, const std::string &p, Layer *L, ui
     return ld.vec(p + "act", {4}, &L->act);
 }
 
+uint32_t env_u32(const char *name, uint32_t dflt) { const char *s = getenv(name); return (s && *s) ? (uint32_t)strtoul(s, nullptr, 10) : dflt; }
+
 // Dynamic-Tanh norm `name`: gain, bias `name`.b, one number `name`.alpha
 int load_dyt(Loader &ld, const std::string &name, uint32_t E, Dyt *n) {
     float *w = nullptr, *b = nullptr; std::vector<float> al; std::vector<uint64_t> sh; int r;
@@ -496,8 +499,13 @@ int load_diff_attn(Loader &ld, const nb::Json *m, const std::string &p, Layer *L
     const bool vec = diff_attn_vec(L->dim, L->vdim, (uint32_t)(H * 2 * D + (L->kv_from < 0 ? G * 2 * D + G * VD : 0)));
     for (uint32_t hpb = std::min<uint32_t>(8u, L->H); hpb >= 1u && !L->a_hpb; hpb = hpb / 2u) {
         const uint32_t ngk = diff_attn_ngk(L->H, L->G, hpb);
-        for (uint32_t qt : {L->vdim <= 128u ? 8u : 4u, 4u, 1u})
+        for (uint32_t qt : {4u, 1u})          // four query tokens per prefill block: 128 registers, two blocks per SM (eight measured 10 % slower at one block per SM)
             if (diff_attn_smem(L->dim, L->vdim, ngk, qt, hpb, vec) <= kDiffSmemMax) { L->a_hpb = hpb; L->a_ngk = ngk; L->a_qt = qt; break; }
+    }
+    if (L->a_hpb) {
+        const uint32_t rep_ = L->H / L->G;
+        L->a_hpb1 = rep_ >= 2u ? std::min(L->a_hpb, rep_) : std::min(L->a_hpb, 4u);
+        L->a_ngk1 = diff_attn_ngk(L->H, L->G, L->a_hpb1);
     }
     if (!L->a_hpb) return fail(NB200_EINVAL, "%s: one key page of a key/value head (%u + %u floats per key) does not fit the attention kernel's shared memory", p.c_str(), 2 * L->dim, L->vdim);
     return 0;
@@ -584,6 +592,8 @@ int gemm(LayeredEngine *e, GemmArgs a, uint32_t groups, uint32_t maxM, bool wf32
         const uint32_t gx = gemv_blocks(e, a.N, active ? std::min(active, groups) : groups);
         if (a.epi == EPI_CONV_RANGES)
             return f32 ? launch<GemmArgs>(e, k_gemv_ext<float, 1>, dim3(gx, groups), dim3(256), 0, a) : launch<GemmArgs>(e, k_gemv_ext<__nv_bfloat16, 1>, dim3(gx, groups), dim3(256), 0, a);
+        if (a.a_parts > 1)
+            return f32 ? launch<GemmArgs>(e, k_gemv_ext<float, 4>, dim3(gx, groups), dim3(256), 0, a) : launch<GemmArgs>(e, k_gemv_ext<__nv_bfloat16, 4>, dim3(gx, groups), dim3(256), 0, a);
         if (a.glu)
             return f32 ? launch<GemmArgs>(e, k_gemv_ext<float, 3>, dim3(gx, groups), dim3(256), 0, a) : launch<GemmArgs>(e, k_gemv_ext<__nv_bfloat16, 3>, dim3(gx, groups), dim3(256), 0, a);
         if (a.a_poly)
@@ -861,13 +871,11 @@ int mix_window_ssm(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &
 template <int VCH>
 int diff_attn_launch_v(LayeredEngine *e, const DiffAttnArgs &a, uint32_t qt, uint32_t hpb, size_t smem) {
     const dim3 grid((a.T + qt - 1) / qt, a.nsplit, (a.H + hpb - 1) / hpb), block(hpb * 32);
-    if (qt == 8) return launch<DiffAttnArgs>(e, k_diff_attn<VCH, 8>, grid, block, smem, a);
     if (qt == 4) return launch<DiffAttnArgs>(e, k_diff_attn<VCH, 4>, grid, block, smem, a);
     return launch<DiffAttnArgs>(e, k_diff_attn<VCH, 1>, grid, block, smem, a);
 }
 template <int VCH>
 int diff_attn_optin_v(int smem) {
-    CK(cudaFuncSetAttribute((const void *)k_diff_attn<VCH, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     CK(cudaFuncSetAttribute((const void *)k_diff_attn<VCH, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     CK(cudaFuncSetAttribute((const void *)k_diff_attn<VCH, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     return 0;
@@ -886,17 +894,18 @@ int mix_diff_attn(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &c
         RopeKvArgs ra{e->b_p, P, QW, QW + KW, has_kv ? 1u : 0u, run.cache, cx.table, T, H, G, 2u, D, VD, L.RL, L.rot_dims, cx.pos0, L.rot_tab, cx.pos_ptr};
         if ((r = launch<RopeKvArgs>(e, k_rope_kv, dim3(T), dim3(256), 0, ra))) return r;
     }
-    DiffAttnArgs aa{e->b_p, P, run.cache, cx.table, e->b_a, T, H, G, D, VD, L.RL, cx.pos0, L.scale, L.lambda, 1.0f - L.diff, e->eps, cx.pos_ptr, 1u, e->b_dpart, e->b_dtick, L.a_ngk};
     const bool small = T <= kGemvMaxM;
+    const uint32_t hpb = small ? L.a_hpb1 : L.a_hpb, ngk = small ? L.a_ngk1 : L.a_ngk;
+    DiffAttnArgs aa{e->b_p, P, run.cache, cx.table, e->b_a, T, H, G, D, VD, L.RL, cx.pos0, L.scale, L.lambda, 1.0f - L.diff, e->eps, cx.pos_ptr, 1u, e->b_dpart, e->b_dtick, ngk};
     if (cx.pos_ptr) aa.nsplit = kSplitMax;           // the position is not known here: splits without keys write empty partials
     else if (small) aa.nsplit = std::max(1u, std::min(kSplitMax, (cx.pos0 + T + kPage - 1) / kPage / 2u));
     const uint32_t qt = small ? 1u : L.a_qt;
-    const size_t smem = diff_attn_smem(D, VD, L.a_ngk, qt, L.a_hpb, diff_attn_vec(D, VD, P));
+    const size_t smem = diff_attn_smem(D, VD, ngk, qt, hpb, diff_attn_vec(D, VD, P));
     switch (diff_vch(VD)) {
-        case 0: r = diff_attn_launch_v<1>(e, aa, qt, L.a_hpb, smem); break;
-        case 1: r = diff_attn_launch_v<2>(e, aa, qt, L.a_hpb, smem); break;
-        case 2: r = diff_attn_launch_v<4>(e, aa, qt, L.a_hpb, smem); break;
-        default: r = diff_attn_launch_v<8>(e, aa, qt, L.a_hpb, smem);
+        case 0: r = diff_attn_launch_v<1>(e, aa, qt, hpb, smem); break;
+        case 1: r = diff_attn_launch_v<2>(e, aa, qt, hpb, smem); break;
+        case 2: r = diff_attn_launch_v<4>(e, aa, qt, hpb, smem); break;
+        default: r = diff_attn_launch_v<8>(e, aa, qt, hpb, smem);
     }
     if (r) return r;
     return gemm(e, plain(e->b_a, H * VD, L.o, e->d, E, T, L.o_b), 1, T);
@@ -915,7 +924,7 @@ int mix_ssd(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &cx) {
         if ((r = gemm(e, pj, 1, T))) return r;
     } else if ((r = gemm(e, plain(e->hm, E, L.proj, e->b_p, Pw, T), 1, T)) ||
                (r = conv_launch(e, ConvArgs{e->b_p + inner, Pw, L.m_conv, L.m_conv_b, cx.st + run.st_conv, e->b_sdx, T, XW, L.m_taps, XW, 1}))) return r;
-    SsdArgs sa{e->b_sdx, XW, e->b_p + inner + XW, Pw, L.dt_b, L.A, L.Dv, cx.st + run.st_S, e->b_sdy, T, Hn, Pd, N, G, 0u, 0u, e->b_sseg};
+    SsdArgs sa{e->b_sdx, XW, e->b_p + inner + XW, Pw, L.dt_b, L.A, L.Dv, cx.st + run.st_S, e->b_sdy, T, Hn, Pd, N, G, 0u, 0u, e->b_sseg, e->b_p, Pw};
     const uint32_t nseg = T >= 64 ? std::min(kRetSegs, T / 32u) : 1u;
     if (nseg > 1) sa.seg_len = (T + nseg - 1u) / nseg;
     // columns per warp: four (fewest staged bytes per FMA) where the grid still gives every SM a dozen warps, else one
@@ -935,8 +944,17 @@ int mix_ssd(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &cx) {
             if ((r = launch<SsdChainArgs>(e, k_ssd_chain, dim3(std::min(8u, (Pd * N + 255u) / 256u), Hn), dim3(256), 0, ca))) return r;
         }
     }
-    SsdOutArgs oa{e->b_sdy, e->b_p, Pw, L.gn, e->b_a, T, inner, L.parts, e->eps};
-    if ((r = launch<SsdOutArgs>(e, k_ssd_out, dim3(T * L.parts), dim3(128), 0, oa))) return r;
+    // the scan's output leaves gated; its norm in equal parts is the prologue of the output product for short portions (where the
+    // parts are multiples of 8 columns), a kernel of its own otherwise
+    const uint32_t plen = inner / L.parts;
+    if (small && (L.parts == 1 || (L.parts <= 32 && plen % 8u == 0))) {
+        GemmArgs o = plain(e->b_sdy, inner, L.o, e->d, E, T);
+        o.a_norm_w = L.gn; o.a_eps = e->eps; o.a_parts = L.parts;
+        if (L.parts == 1) o.a_parts = 0;          // one part: the plain instance's whole-row norm
+        return gemm(e, o, 1, T);
+    }
+    GroupNormArgs oa{e->b_sdy, L.gn, e->b_a, T, inner, L.parts, e->eps};
+    if ((r = launch<GroupNormArgs>(e, k_group_norm, dim3(T * L.parts), dim3(small ? 1024 : 128), 0, oa))) return r;
     return gemm(e, plain(e->b_a, inner, L.o, e->d, E, T), 1, T);
 }
 
@@ -1114,7 +1132,8 @@ int embed_tokens(LayeredEngine *e, uint32_t slot, const uint32_t *tok_dev, uint3
         e->cur = e->stream;
         EmbedPairArgs a{tok_dev, pos_ptr, e->embed.p, e->pairs.p, e->x, e->hm, reinterpret_cast<uint32_t *>(e->state + (size_t)slot * e->slot_floats + e->st_tok),
                         T, e->E, e->buckets, e->mul_prev, e->mul_cur, e->emb_scale, e->embed_norm, e->layers[e->runs[0].layer].d1};
-        return e->f32 ? launch<EmbedPairArgs>(e, k_embed_pair<float>, dim3(T), dim3(128), 0, a) : launch<EmbedPairArgs>(e, k_embed_pair<__nv_bfloat16>, dim3(T), dim3(128), 0, a);
+        const dim3 block(T <= kGemvMaxM && e->E >= 2048 ? 512 : (T <= kGemvMaxM && e->E >= 1024 ? 256 : 128));
+        return e->f32 ? launch<EmbedPairArgs>(e, k_embed_pair<float>, dim3(T), block, 0, a) : launch<EmbedPairArgs>(e, k_embed_pair<__nv_bfloat16>, dim3(T), block, 0, a);
     }
     if (e->max_pos) {      // a learned position row joins the token row
         if (e->f32) k_embed_pos<float><<<T, 128, 0, e->stream>>>(tok_dev, pos_ptr, (const float *)e->embed.p, (const float *)e->pos_table.p, e->x, e->E, pos0);
@@ -1514,7 +1533,6 @@ void lm_destroy(nb200_engine *h) {
 const nb::EngineOps kLayeredOps = {lm_destroy, lm_get_config, lm_forward, lm_read_logits, lm_next_greedy, lm_next_sampled, lm_decode_greedy,
                                    lm_seq_open, lm_seq_close, lm_step, lm_read_residual, lm_step_timed};
 
-uint32_t env_u32(const char *name, uint32_t dflt) { const char *s = getenv(name); return (s && *s) ? (uint32_t)strtoul(s, nullptr, 10) : dflt; }
 
 int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
     const nb::Json &cfg = dir->config;
@@ -1689,10 +1707,10 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
         if (L.ff_kind == FF_DENSE_POLY) sF = std::max(sF, L.ff);
         if (L.type == MIX_DIFF_ATTN) {
             sP = std::max(sP, L.H * 2 * L.dim + (L.kv_from < 0 ? L.G * (2 * L.dim + L.vdim) : 0u)); sA = std::max(sA, L.H * L.vdim);
-            sDP = std::max(sDP, L.H * 2 * (L.vdim + 2)); sDT = std::max(sDT, (L.H + L.a_hpb - 1) / L.a_hpb);
+            sDP = std::max(sDP, L.H * 2 * (L.vdim + 2)); sDT = std::max(sDT, (L.H + L.a_hpb1 - 1) / L.a_hpb1);
             const bool vec = diff_attn_vec(L.dim, L.vdim, L.H * 2 * L.dim + (L.kv_from < 0 ? L.G * (2 * L.dim + L.vdim) : 0u));
             size_t &sm = diff_smem[diff_vch(L.vdim)];
-            sm = std::max(sm, std::max(diff_attn_smem(L.dim, L.vdim, L.a_ngk, L.a_qt, L.a_hpb, vec), diff_attn_smem(L.dim, L.vdim, L.a_ngk, 1, L.a_hpb, vec)));
+            sm = std::max(sm, std::max(diff_attn_smem(L.dim, L.vdim, L.a_ngk, L.a_qt, L.a_hpb, vec), diff_attn_smem(L.dim, L.vdim, L.a_ngk1, 1, L.a_hpb1, vec)));
         }
         if (L.type == MIX_SSD) {
             const uint32_t inner = L.H * L.vdim, XW = inner + 2 * L.G * L.mN;

@@ -73,6 +73,9 @@ struct GemmArgs {
     // act(s g_n) (s u_n) with g_n, u_n the products of rows n and N + n and s = row_scale[row] (1 when null): a routed expert whose
     // input is weighted by the router's score, without a pass over the input.
     uint32_t glu; const float *row_scale;
+    // k_gemv only.  Prologue (with a_norm_w): a_parts > 1 norms row r of A in a_parts equal parts, each by its own root mean square
+    // (K / a_parts columns each, a multiple of 8; at most 32 parts).
+    uint32_t a_parts;
 };
 
 // Programmatic dependent launch: every kernel first lets the NEXT kernel of its stream be scheduled (its blocks then sit in their own
@@ -356,9 +359,11 @@ __device__ __forceinline__ void conv_range_rows(const GemmArgs::ConvRange &r, ui
 // c / rms(z^3), e) of row i; rnd: round the activation to bf16 first.
 struct PolyRow { float r1, r2, r3, e; };
 __device__ __forceinline__ float poly_of(float x, const PolyRow &p) { return fmaf(p.r1, x, fmaf(p.r2, x * x, fmaf(p.r3, x * x * x, p.e))); }
-template <typename WT, bool POLY = false>
+// GN: the scale of row i at column k is gsc[i * 32 + k / plen] (a norm in equal parts) instead of sc[i]
+template <typename WT, bool POLY = false, bool GN = false>
 __device__ __forceinline__ void warp_dots(const WT *wr, const float *(&ap)[kGemvMaxM], uint32_t rows, uint32_t K, uint32_t kvec, const float (&sc)[kGemvMaxM],
-                                          const float *nw, bool rnd, uint32_t lane, float (&acc)[kGemvMaxM], const PolyRow *pc = nullptr) {
+                                          const float *nw, bool rnd, uint32_t lane, float (&acc)[kGemvMaxM], const PolyRow *pc = nullptr,
+                                          const float *gsc = nullptr, uint32_t plen = 1) {
     constexpr uint32_t VN = WVec<WT>::N;
 #pragma unroll
     for (uint32_t i = 0; i < kGemvMaxM; i++) acc[i] = 0.0f;
@@ -372,7 +377,10 @@ __device__ __forceinline__ void warp_dots(const WT *wr, const float *(&ap)[kGemv
 #pragma unroll
                 for (uint32_t j = 0; j < VN; j += 4) {
                     float4 x = *reinterpret_cast<const float4 *>(ap[i] + k + j);
-                    if (nw) { const float4 g = __ldg(reinterpret_cast<const float4 *>(nw + k + j)); x.x = x.x * sc[i] * g.x; x.y = x.y * sc[i] * g.y; x.z = x.z * sc[i] * g.z; x.w = x.w * sc[i] * g.w; }
+                    if (nw) {
+                        const float si = GN ? gsc[i * 32u + (k + j) / plen] : sc[i];
+                        const float4 g = __ldg(reinterpret_cast<const float4 *>(nw + k + j)); x.x = x.x * si * g.x; x.y = x.y * si * g.y; x.z = x.z * si * g.z; x.w = x.w * si * g.w;
+                    }
                     if (POLY && pc) { x.x = poly_of(x.x, pc[i]); x.y = poly_of(x.y, pc[i]); x.z = poly_of(x.z, pc[i]); x.w = poly_of(x.w, pc[i]); }
                     if (rnd) { x.x = round_bf16(x.x); x.y = round_bf16(x.y); x.z = round_bf16(x.z); x.w = round_bf16(x.w); }
                     acc[i] = fmaf(w[j], x.x, acc[i]); acc[i] = fmaf(w[j + 1], x.y, acc[i]);
@@ -387,7 +395,7 @@ __device__ __forceinline__ void warp_dots(const WT *wr, const float *(&ap)[kGemv
         for (uint32_t i = 0; i < kGemvMaxM; i++)
             if (i < rows) {
                 float x = ap[i][k];
-                if (nw) x = x * sc[i] * nw[k];
+                if (nw) x = x * (GN ? gsc[i * 32u + k / plen] : sc[i]) * nw[k];
                 if (POLY && pc) x = poly_of(x, pc[i]);
                 acc[i] = fmaf(w, rnd ? round_bf16(x) : x, acc[i]);
             }
@@ -398,8 +406,8 @@ __device__ __forceinline__ void warp_dots(const WT *wr, const float *(&ap)[kGemv
         for (int o = 16; o > 0; o >>= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
 }
 
-// EXT 1: the instance that also knows the convolution-range epilogue, EXT 2: the PolyNorm prologue, EXT 3: the gated pair (registers
-// the plain one keeps)
+// EXT 1: the instance that also knows the convolution-range epilogue, EXT 2: the PolyNorm prologue, EXT 3: the gated pair, EXT 4: the
+// norm in equal parts (registers the plain one keeps)
 template <typename WT, int EXT = 0>
 __device__ __forceinline__ void gemv_body(const GemmArgs &a, float *red) {
     const GroupView gv = group_view(a, blockIdx.y);
@@ -418,7 +426,20 @@ __device__ __forceinline__ void gemv_body(const GemmArgs &a, float *red) {
         vec = vec && ((reinterpret_cast<uintptr_t>(ap[i]) & 15u) == 0);
         sc[i] = 1.0f;
     }
-    if (a.a_norm_w) {          // rows is the same for every thread of the block
+    __shared__ float gsc[EXT == 4 ? kGemvMaxM * 32 : 1];
+    const uint32_t plen = EXT == 4 ? a.K / a.a_parts : 1u;
+    if (EXT == 4) {          // a warp per (row, part): the part's root mean square
+        for (uint32_t job = threadIdx.x >> 5; job < rows * a.a_parts; job += blockDim.x >> 5) {
+            const uint32_t i = job / a.a_parts, p = job % a.a_parts;
+            const float *src = a.A + (size_t)(a.a_rows ? a.a_rows[gv.r0 + i] : gv.r0 + i) * a.lda + gv.a0 + p * plen;
+            float s = 0.0f;
+            for (uint32_t k = lane * 4u; k < plen; k += 128u) { const float4 q = *reinterpret_cast<const float4 *>(src + k); s = fmaf(q.x, q.x, fmaf(q.y, q.y, fmaf(q.z, q.z, fmaf(q.w, q.w, s)))); }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (lane == 0) gsc[i * 32u + p] = 1.0f / sqrtf(s / (float)plen + a.a_eps);
+        }
+        __syncthreads();
+    } else if (a.a_norm_w) {          // rows is the same for every thread of the block
 #pragma unroll
         for (uint32_t i = 0; i < kGemvMaxM; i++)
             if (i < rows) {
@@ -451,7 +472,7 @@ __device__ __forceinline__ void gemv_body(const GemmArgs &a, float *red) {
     const uint32_t kvec = vec ? (a.K / WVec<WT>::N) * WVec<WT>::N : 0u;
     for (uint32_t n = warp0; n < a.N; n += nwarps) {
         float acc[kGemvMaxM];
-        warp_dots<WT, EXT == 2>(W + (size_t)n * a.ldw, ap, rows, a.K, kvec, sc, a.a_norm_w, a.round_a != 0, lane, acc, (EXT == 2 && a.a_poly) ? pc : nullptr);
+        warp_dots<WT, EXT == 2, EXT == 4>(W + (size_t)n * a.ldw, ap, rows, a.K, kvec, sc, a.a_norm_w, a.round_a != 0, lane, acc, (EXT == 2 && a.a_poly) ? pc : nullptr, gsc, plen);
         if (EXT == 3) {          // the up row of the pair, then act(s g) (s u)
             float up[kGemvMaxM];
             warp_dots<WT, false>(W + (size_t)(a.N + n) * a.ldw, ap, rows, a.K, kvec, sc, nullptr, a.round_a != 0, lane, up);

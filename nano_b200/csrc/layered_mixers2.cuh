@@ -14,7 +14,7 @@
 //                        o = a1 - lambda a2, unit RMS over the head, fixed output scale; key splits for short portions)
 //   state-space duality  k_ssd_scan (Mamba-2: one decay per head and token, S <- a_t S + dt_t B_t x_t^T, y = S^T C_t + D x_t; fp32
 //                        state [head][value column][state coordinate]; long portions as time segments side by side with
-//                        k_ssd_chain between the two passes), k_ssd_out (y silu(z), unit RMS in equal parts, vector gain)
+//                        k_ssd_chain between the two passes; the output leaves gated, y silu(z)), k_group_norm (unit RMS in equal parts, vector gain)
 //   feed-forward         k_glu (act(s g) (s u) over [gate | up] rows, s an optional per-row scale: a routed expert whose INPUT is
 //                        weighted by the router's score)
 #pragma once
@@ -35,7 +35,7 @@ struct EmbedPairArgs {
     uint32_t T, E, buckets, mul_prev, mul_cur; float scale; Dyt norm, next;
 };
 template <typename WT>
-__global__ void __launch_bounds__(128) k_embed_pair(const EmbedPairArgs a) {
+__global__ void __launch_bounds__(512) k_embed_pair(const EmbedPairArgs a) {
     pdl_enter();
     const uint32_t t = blockIdx.x, off = a.pos_ptr ? *a.pos_ptr : 0u;
     const uint32_t tok = a.tokens[t + off];
@@ -183,7 +183,8 @@ __global__ void __launch_bounds__(256) k_diff_attn(const DiffAttnArgs a) {
     extern __shared__ __align__(16) float sm[];
     const uint32_t hpb = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t H = a.H, D = a.D, D2 = 2u * D, VD = a.VD, rep = H / a.G;
-    const uint32_t tq0 = blockIdx.x * QT, nq = min((uint32_t)QT, a.T - tq0), split = blockIdx.y, h0 = blockIdx.z * hpb, h = h0 + warp;
+    // the last query tile sees the most keys: tiles are handed out from the end, so the longest blocks start first
+    const uint32_t tq0 = (gridDim.x - 1u - blockIdx.x) * QT, nq = min((uint32_t)QT, a.T - tq0), split = blockIdx.y, h0 = blockIdx.z * hpb, h = h0 + warp;
     const uint32_t g_lo = h0 / rep, ng = (min(H, h0 + hpb) - 1u) / rep - g_lo + 1u;
     const bool vec = diff_attn_vec(D, VD, a.ldq);
     const uint32_t KW = ng * D2, VW = ng * VD, LDK = diff_attn_ldk(a.ngk * D2, vec), LDV = a.ngk * VD;
@@ -372,6 +373,7 @@ __global__ void __launch_bounds__(256) k_diff_attn(const DiffAttnArgs a) {
 struct SsdArgs {
     const float *xbc; uint32_t ldx; const float *dt; uint32_t lddt; const float *dt_bias, *rate, *Dv;
     float *S; float *y; uint32_t T, Hn, P, N, G; uint32_t mode, seg_len; float *seg_S;
+    const float *z; uint32_t ldz;      // the gate: what is written is y silu(z[t][h P + j])
 };
 __device__ __forceinline__ float ssd_decay(float rate, float dt) { return (float)exp(-(double)rate * (double)dt); }
 template <int DCH, int CPW>
@@ -436,6 +438,7 @@ __global__ void __launch_bounds__(256) k_ssd_scan(const SsdArgs a) {
                 for (uint32_t i = 0; i < CPW; i++) { S[i][c] = fmaf(av, S[i][c], bn * v[i]); acc[i] = fmaf(S[i][c], cn, acc[i]); }
             }
             float *yrow = a.y + (size_t)(t0 + t) * a.Hn * a.P + xoff + jw;
+            const float *zrow = a.z + (size_t)(t0 + t) * a.ldz + xoff + jw;
             if (CPW == 4) {
                 // four sums over the warp with six shuffles: halves of the warp trade two columns, quarters one, then eight lanes add up;
                 // lanes 0, 8, 16, 24 end with columns 0, 1, 2, 3
@@ -445,14 +448,14 @@ __global__ void __launch_bounds__(256) k_ssd_scan(const SsdArgs a) {
                 float k = (h8 ? k1 : k0) + __shfl_xor_sync(0xffffffffu, h8 ? k0 : k1, 8);
                 k += __shfl_xor_sync(0xffffffffu, k, 4); k += __shfl_xor_sync(0xffffffffu, k, 2); k += __shfl_xor_sync(0xffffffffu, k, 1);
                 const uint32_t col = lane >> 3;
-                if ((lane & 7u) == 0 && jw + col < a.P) yrow[col] = fmaf(Dh, xr[t][warp * CPW + col], k);
+                if ((lane & 7u) == 0 && jw + col < a.P) yrow[col] = fmaf(Dh, xr[t][warp * CPW + col], k) * siluf_(zrow[col]);
             } else {
 #pragma unroll
                 for (uint32_t i = 0; i < CPW; i++) acc[i] = warp_sum(acc[i]);
                 float mine = acc[0];
 #pragma unroll
                 for (uint32_t i = 1; i < CPW; i++) if (lane == i) mine = acc[i];
-                if (lane < CPW && jw + lane < a.P) yrow[lane] = fmaf(Dh, xr[t][warp * CPW + lane], mine);
+                if (lane < CPW && jw + lane < a.P) yrow[lane] = fmaf(Dh, xr[t][warp * CPW + lane], mine) * siluf_(zrow[lane]);
             }
         }
     }
@@ -499,20 +502,20 @@ __global__ void __launch_bounds__(256) k_ssd_chain(const SsdChainArgs a) {
     }
 }
 
-// gate, group norm and gain of the scan's output: u = y silu(z); every one of the `parts` equal parts of a token's row is divided by
-// its own root mean square (eps inside the root) and multiplied by the gain.  One block per (token, part).
-struct SsdOutArgs { const float *y; const float *z; uint32_t ldz; const float *gain; float *out; uint32_t T, C, parts; float eps; };
-__global__ void __launch_bounds__(128) k_ssd_out(const SsdOutArgs a) {
+// group norm and gain: every one of the `parts` equal parts of a token's row is divided by its own root mean square (eps inside the
+// root) and multiplied by the gain.  One block per (token, part).  (Short portions: the prologue of the product that follows, GemmArgs::a_parts.)
+struct GroupNormArgs { const float *y; const float *gain; float *out; uint32_t T, C, parts; float eps; };
+__global__ void __launch_bounds__(1024) k_group_norm(const GroupNormArgs a) {
     pdl_enter();
     __shared__ float red[32];
     const uint32_t t = blockIdx.x / a.parts, part = blockIdx.x % a.parts, W = a.C / a.parts, c0 = part * W;
-    const float *y = a.y + (size_t)t * a.C + c0, *z = a.z + (size_t)t * a.ldz + c0;
+    const float *y = a.y + (size_t)t * a.C + c0;
     float s = 0.0f;
-    for (uint32_t i = threadIdx.x; i < W; i += blockDim.x) { const float u = y[i] * siluf_(z[i]); s = fmaf(u, u, s); }
+    for (uint32_t i = threadIdx.x; i < W; i += blockDim.x) s = fmaf(y[i], y[i], s);
     s = block_sum(s, red);
     const float rinv = 1.0f / sqrtf(s / (float)W + a.eps);
     float *out = a.out + (size_t)t * a.C + c0;
-    for (uint32_t i = threadIdx.x; i < W; i += blockDim.x) out[i] = y[i] * siluf_(z[i]) * rinv * a.gain[c0 + i];
+    for (uint32_t i = threadIdx.x; i < W; i += blockDim.x) out[i] = y[i] * rinv * a.gain[c0 + i];
 }
 
 }  // namespace lm
