@@ -144,6 +144,7 @@ def test_nano_cli_binary_starts_and_reports_missing_model():
     assert b"open" in r.stderr.lower() or b"couldn" in r.stderr.lower()
 
 
+@needs_refhost
 def test_q4k_tensor_functions_through_reference_names():
     """tensor.h:160-166 as the reference's tools/export_q4k.c calls them (quantize_tensor_q4k -> matmul_q4k on a 3-D
     weight with a layer index), against the outputs committed from the unmodified reference and the oracle."""

@@ -72,3 +72,42 @@ def test_rakarax_oracle_is_causal_and_windowed():
     other = forward(cfg, w, t2)
     # window 3 and two taps: position 5 reaches positions 5 .. 5 + 2 + 1 through the attention, not beyond
     assert np.abs(other[5] - full[5]).max() > 1e-6 and np.allclose(other[9:], full[9:], atol=1e-12)
+
+
+GOK_ATT = {"heads": 2, "kv_heads": 1, "dim": 8, "vdim": 8, "scale": 0.4, "diff": 0.3, "rot": {"dims": 4, "base": 100.0}}
+GOK_SSD = {"heads": 2, "vdim": 4, "state": 3, "groups": 1, "conv": 2, "norm_groups": 1}
+
+
+@pytest.mark.skipif(E.device_count() > 0, reason="box has a GPU")
+def test_gokinex_folder_reaches_the_layered_family(tmp_path):
+    cfg = md.gokinex_config(16, 8, [("attention", GOK_ATT, {"kind": "dense", "ff": 12}), ("attention", dict(GOK_ATT, kv_from=0), None)], bigram={"buckets": 5, "mul_prev": 3, "mul_cur": 2})
+    w = md.gokinex_random(cfg)
+    assert "l0.mix.k" in w and "l1.mix.q" in w and "l1.mix.k" not in w and "l1.mix.v" not in w      # a layer with kv_from has no key/value projections
+    assert w["bigram"].shape == (6, 8)                                                            # one more row, for the first token
+    p = md.write_model_dir(str(tmp_path / "g"), cfg, w)
+    with pytest.raises(E.NB200Error, match="no CUDA device"):
+        E.Engine(p, 16)
+
+
+def test_gokinex_oracle_is_causal_and_reads_what_it_should():
+    """The plain restatement itself: a prefix gives the same logits; the pair table sees the previous token and only that one; a
+    scan with a fast decay forgets; lambda 0 with equal maps leaves the first map alone."""
+    import gokinex_oracle as O
+    cfg = md.gokinex_config(20, 16, [("mamba2", GOK_SSD, None), ("attention", GOK_ATT, {"kind": "moe", "router": {"experts": 3, "top": 1}, "expert": {"ff": 6}, "shared": {"ff": 4}})],
+                            scale=2.0, bigram={"buckets": 7, "mul_prev": 3, "mul_cur": 2})
+    w = md.gokinex_random(cfg, 3)
+    t = np.random.default_rng(0).integers(0, 20, 24)
+    full = O.forward(cfg, w, t)
+    assert np.allclose(O.forward(cfg, w, t[:10]), full[:10], atol=1e-12)
+    tt = {k: v.astype(np.float64) for k, v in w.items()}
+    e = O.embed(cfg, tt, t)
+    t2 = t.copy(); t2[5] = (t2[5] + 1) % 20
+    e2 = O.embed(cfg, tt, t2)
+    changed = np.abs(e2 - e).max(-1) > 0
+    assert changed[5] and changed[6] and not changed[:5].any() and not changed[7:].any()
+    assert np.allclose(O.embed(cfg, tt, t[3:])[0], O.dyt(tt["embed"][t[3]] * 2.0 + tt["bigram"][7], tt, "embed.norm"))      # a first token takes the last row
+    # interleaved pairs: rotating by position p equals a complex multiplication of (x[2i] + i x[2i+1])
+    u = np.random.default_rng(1).standard_normal((3, 2, 8))
+    r = O.rotate(u, {"dims": 4, "base": 100.0}, [0, 1, 5])
+    z = (u[2, 1, 2] + 1j * u[2, 1, 3]) * np.exp(1j * 5 * 100.0 ** (-2.0 / 4))
+    assert np.allclose([r[2, 1, 2], r[2, 1, 3]], [z.real, z.imag]) and np.array_equal(r[..., 4:], u[..., 4:]) and np.allclose(r[0], u[0])
