@@ -178,7 +178,7 @@ __device__ __forceinline__ void diff_finish(const DiffAttnArgs &a, const float (
     for (int c = 0; c < VCH; c++) { const uint32_t r = lane + 32u * c; if (r < a.VD) a.out[(t * a.H + h) * a.VD + r] = dv[c] * f; }
 }
 template <int VCH, int QT>
-__global__ void __launch_bounds__(256) k_diff_attn(const DiffAttnArgs a) {
+__global__ void __launch_bounds__(256, QT > 1 && VCH <= 4 ? 2 : 1) k_diff_attn(const DiffAttnArgs a) {
     pdl_enter();
     extern __shared__ __align__(16) float sm[];
     const uint32_t hpb = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -215,14 +215,24 @@ __global__ void __launch_bounds__(256) k_diff_attn(const DiffAttnArgs a) {
         const uint32_t nk = min(kPage, nkeys - tile * kPage);
         const float *ksrc = src + g_lo * D2, *vsrc = src + a.G * D2 + g_lo * VD;
         if (vec) {
-            const uint32_t kw4 = KW / 4u, vw4 = VW / 4u;
-            for (uint32_t i = threadIdx.x; i < nk * kw4; i += blockDim.x) {
-                const uint32_t key = i / kw4, c4 = i % kw4;
-                *reinterpret_cast<float4 *>(k_s + key * LDK + c4 * 4u) = __ldg(reinterpret_cast<const float4 *>(ksrc + (size_t)key * a.RL) + c4);
-            }
-            for (uint32_t i = threadIdx.x; i < nk * vw4; i += blockDim.x) {
-                const uint32_t key = i / vw4, c4 = i % vw4;
-                *reinterpret_cast<float4 *>(v_s + key * LDV + c4 * 4u) = __ldg(reinterpret_cast<const float4 *>(vsrc + (size_t)key * a.RL) + c4);
+            // keys and values of the tile as one list of 16-byte pieces; a thread of a short portion's block (few warps, nothing else to
+            // hide the latency behind) has eight of them in flight at once, a prefill block two (registers: two blocks per SM)
+            constexpr int NB = QT == 1 ? 8 : 2;
+            const uint32_t kw4 = KW / 4u, vw4 = VW / 4u, nk4 = nk * kw4, n4 = nk4 + nk * vw4;
+            for (uint32_t base = 0; base < n4; base += NB * blockDim.x) {
+                float4 v[NB];
+#pragma unroll
+                for (int k = 0; k < NB; k++) {
+                    const uint32_t i = base + k * blockDim.x + threadIdx.x;
+                    if (i < nk4) v[k] = __ldg(reinterpret_cast<const float4 *>(ksrc + (size_t)(i / kw4) * a.RL) + i % kw4);
+                    else if (i < n4) v[k] = __ldg(reinterpret_cast<const float4 *>(vsrc + (size_t)((i - nk4) / vw4) * a.RL) + (i - nk4) % vw4);
+                }
+#pragma unroll
+                for (int k = 0; k < NB; k++) {
+                    const uint32_t i = base + k * blockDim.x + threadIdx.x;
+                    if (i < nk4) *reinterpret_cast<float4 *>(k_s + (i / kw4) * LDK + (i % kw4) * 4u) = v[k];
+                    else if (i < n4) *reinterpret_cast<float4 *>(v_s + ((i - nk4) / vw4) * LDV + ((i - nk4) % vw4) * 4u) = v[k];
+                }
             }
         } else {
             for (uint32_t i = threadIdx.x; i < nk * KW; i += blockDim.x) k_s[(i / KW) * LDK + i % KW] = ksrc[(size_t)(i / KW) * a.RL + i % KW];
@@ -335,25 +345,29 @@ __global__ void __launch_bounds__(256) k_diff_attn(const DiffAttnArgs a) {
     for (int qi = 0; qi < QT; qi++) {
         if ((uint32_t)qi >= nq) continue;
         const size_t t = tq0 + qi;
-        float acc[2][VCH], inv[2];
+        float acc[2][VCH], inv[2], w[2];
+        const float *base = a.part + ((size_t)t * a.nsplit * H + h) * 2u * PW;
 #pragma unroll
         for (int mp = 0; mp < 2; mp++) {
-            const float *base = a.part + (((size_t)t * a.nsplit * H + h) * 2u + mp) * PW;
             const bool live = lane < a.nsplit;
-            const float ls = live ? __ldcg(base + lane * stride + VD + 1u) : 0.0f;
-            const float ms = (live && ls > 0.0f) ? __ldcg(base + lane * stride + VD) : -INFINITY;
+            const float ls = live ? __ldcg(base + lane * stride + mp * PW + VD + 1u) : 0.0f;
+            const float ms = (live && ls > 0.0f) ? __ldcg(base + lane * stride + mp * PW + VD) : -INFINITY;
             float M = ms;
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
-            const float w = ls > 0.0f ? expf(ms - M) : 0.0f;
-            inv[mp] = 1.0f / warp_sum(w * ls);
+            w[mp] = ls > 0.0f ? expf(ms - M) : 0.0f;
+            inv[mp] = 1.0f / warp_sum(w[mp] * ls);
 #pragma unroll
             for (int c = 0; c < VCH; c++) acc[mp][c] = 0.0f;
-            for (uint32_t sp = 0; sp < a.nsplit; sp++) {
-                const float ws = __shfl_sync(0xffffffffu, w, sp);
-                if (ws == 0.0f) continue;          // a split without keys wrote nothing of weight (uniform over the warp)
+        }
+        // every split wrote its triples in this launch (zeros where it saw no key), so the loop needs no branch and its loads overlap
+#pragma unroll 4
+        for (uint32_t sp = 0; sp < a.nsplit; sp++) {
+            const float w0 = __shfl_sync(0xffffffffu, w[0], sp), w1 = __shfl_sync(0xffffffffu, w[1], sp);
 #pragma unroll
-                for (int c = 0; c < VCH; c++) { const uint32_t r = lane + 32u * c; if (r < VD) acc[mp][c] = fmaf(ws, __ldcg(base + sp * stride + r), acc[mp][c]); }
+            for (int c = 0; c < VCH; c++) {
+                const uint32_t r = lane + 32u * c;
+                if (r < VD) { acc[0][c] = fmaf(w0, __ldcg(base + sp * stride + r), acc[0][c]); acc[1][c] = fmaf(w1, __ldcg(base + sp * stride + PW + r), acc[1][c]); }
             }
         }
         diff_finish<VCH>(a, acc[0], acc[1], inv[0], inv[1], t, h, lane);
@@ -380,7 +394,7 @@ template <int DCH, int CPW>
 __global__ void __launch_bounds__(256) k_ssd_scan(const SsdArgs a) {
     pdl_enter();
     constexpr uint32_t kCols = 8 * CPW, kTile = DCH <= 4 ? 32 : 16;
-    __shared__ float Bs[kTile][DCH * 32], Cs[kTile][DCH * 32], xs[kTile][kCols], xr[kTile][kCols], as[kTile], ds[kTile];
+    __shared__ float Bs[kTile][DCH * 32], Cs[kTile][DCH * 32], xs[kTile][kCols], xr[kTile][kCols], zs[kTile][kCols], as[kTile], ds[kTile];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, h = blockIdx.y, j0 = blockIdx.x * kCols, jw = j0 + warp * CPW;
     const uint32_t g = h / (a.Hn / a.G), xoff = h * a.P, boff = a.Hn * a.P + g * a.N, coff = a.Hn * a.P + (a.G + g) * a.N;
     float *Sio = a.mode ? a.seg_S + (size_t)blockIdx.z * a.Hn * a.P * a.N : a.S;
@@ -409,6 +423,7 @@ __global__ void __launch_bounds__(256) k_ssd_scan(const SsdArgs a) {
             const uint32_t t = i / kCols, j = i % kCols;
             const float v = j0 + j < a.P ? a.xbc[(size_t)(t0 + t) * a.ldx + xoff + j0 + j] : 0.0f;
             xr[t][j] = v; xs[t][j] = v * ds[t];
+            if (a.mode != 1u) zs[t][j] = j0 + j < a.P ? siluf_(a.z[(size_t)(t0 + t) * a.ldz + xoff + j0 + j]) : 0.0f;
         }
         __syncthreads();
         if (a.mode == 1u) {          // the first pass of a long portion only builds states
@@ -438,7 +453,6 @@ __global__ void __launch_bounds__(256) k_ssd_scan(const SsdArgs a) {
                 for (uint32_t i = 0; i < CPW; i++) { S[i][c] = fmaf(av, S[i][c], bn * v[i]); acc[i] = fmaf(S[i][c], cn, acc[i]); }
             }
             float *yrow = a.y + (size_t)(t0 + t) * a.Hn * a.P + xoff + jw;
-            const float *zrow = a.z + (size_t)(t0 + t) * a.ldz + xoff + jw;
             if (CPW == 4) {
                 // four sums over the warp with six shuffles: halves of the warp trade two columns, quarters one, then eight lanes add up;
                 // lanes 0, 8, 16, 24 end with columns 0, 1, 2, 3
@@ -448,14 +462,14 @@ __global__ void __launch_bounds__(256) k_ssd_scan(const SsdArgs a) {
                 float k = (h8 ? k1 : k0) + __shfl_xor_sync(0xffffffffu, h8 ? k0 : k1, 8);
                 k += __shfl_xor_sync(0xffffffffu, k, 4); k += __shfl_xor_sync(0xffffffffu, k, 2); k += __shfl_xor_sync(0xffffffffu, k, 1);
                 const uint32_t col = lane >> 3;
-                if ((lane & 7u) == 0 && jw + col < a.P) yrow[col] = fmaf(Dh, xr[t][warp * CPW + col], k) * siluf_(zrow[col]);
+                if ((lane & 7u) == 0 && jw + col < a.P) yrow[col] = fmaf(Dh, xr[t][warp * CPW + col], k) * zs[t][warp * CPW + col];
             } else {
 #pragma unroll
                 for (uint32_t i = 0; i < CPW; i++) acc[i] = warp_sum(acc[i]);
                 float mine = acc[0];
 #pragma unroll
                 for (uint32_t i = 1; i < CPW; i++) if (lane == i) mine = acc[i];
-                if (lane < CPW && jw + lane < a.P) yrow[lane] = fmaf(Dh, xr[t][warp * CPW + lane], mine) * siluf_(zrow[lane]);
+                if (lane < CPW && jw + lane < a.P) yrow[lane] = fmaf(Dh, xr[t][warp * CPW + lane], mine) * zs[t][warp * CPW + lane];
             }
         }
     }
