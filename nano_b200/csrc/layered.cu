@@ -144,6 +144,8 @@ struct LayeredEngine : nb::EngineBase {
     // Dynamic-Tanh designs: embedding scale, the pair table and its hash, the norms around the stack, where a slot keeps the last token
     int norm_kind = NORM_RMS_ZERO; float emb_scale = 1.0f; Weight pairs; uint32_t buckets = 0, mul_prev = 0, mul_cur = 0; Dyt embed_norm{}, final_dyt{}; size_t st_tok = 0;
     std::vector<std::pair<std::string, float2 *>> rot_tabs;      // position tables of the rotary attention layers, one per distinct setting
+    // short portions of a Dynamic-Tanh design: the residual update that follows a sublayer rides on the sublayer's last product
+    struct ResEpi { bool on = false; Dyt post{}, pre{}; float *out = nullptr, *keep = nullptr; } res;
     float *b_dpart = nullptr, *b_sseg = nullptr, *b_sdx = nullptr, *b_sdy = nullptr, *b_f2 = nullptr, *b_hg = nullptr, *b_sh2 = nullptr, *b_sg = nullptr, *b_wrow = nullptr; uint32_t *b_dtick = nullptr;
     uint32_t *ids_dev = nullptr, *want_dev = nullptr, *next_dev = nullptr, *tok_host = nullptr; uint8_t *seen = nullptr;
     uint32_t last_T = 0;
@@ -592,6 +594,8 @@ int gemm(LayeredEngine *e, GemmArgs a, uint32_t groups, uint32_t maxM, bool wf32
         const uint32_t gx = gemv_blocks(e, a.N, active ? std::min(active, groups) : groups);
         if (a.epi == EPI_CONV_RANGES)
             return f32 ? launch<GemmArgs>(e, k_gemv_ext<float, 1>, dim3(gx, groups), dim3(256), 0, a) : launch<GemmArgs>(e, k_gemv_ext<__nv_bfloat16, 1>, dim3(gx, groups), dim3(256), 0, a);
+        if (a.res_x && a.a_parts <= 1)
+            return f32 ? launch<GemmArgs>(e, k_gemv_ext<float, 5>, dim3(gx, groups), dim3(256), 0, a) : launch<GemmArgs>(e, k_gemv_ext<__nv_bfloat16, 5>, dim3(gx, groups), dim3(256), 0, a);
         if (a.a_parts > 1)
             return f32 ? launch<GemmArgs>(e, k_gemv_ext<float, 4>, dim3(gx, groups), dim3(256), 0, a) : launch<GemmArgs>(e, k_gemv_ext<__nv_bfloat16, 4>, dim3(gx, groups), dim3(256), 0, a);
         if (a.glu)
@@ -867,6 +871,16 @@ int mix_window_ssm(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &
     return 0;
 }
 
+// a sublayer's last product (into e->d); with the residual epilogue armed it updates e->x and writes the next sublayer's input instead
+int last_product(LayeredEngine *e, GemmArgs g, uint32_t T) {
+    if (e->res.on) {
+        g.res_x = e->x; g.res_out = e->res.out; g.res_keep = e->res.keep;
+        g.res_pw = e->res.post.w; g.res_pb = e->res.post.b; g.res_pa = e->res.post.alpha;
+        g.res_nw = e->res.pre.w; g.res_nb = e->res.pre.b; g.res_na = e->res.pre.alpha;
+    }
+    return gemm(e, g, 1, T);
+}
+
 // ---- grouped-query differential attention ----
 template <int VCH>
 int diff_attn_launch_v(LayeredEngine *e, const DiffAttnArgs &a, uint32_t qt, uint32_t hpb, size_t smem) {
@@ -908,7 +922,7 @@ int mix_diff_attn(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &c
         default: r = diff_attn_launch_v<8>(e, aa, qt, hpb, smem);
     }
     if (r) return r;
-    return gemm(e, plain(e->b_a, H * VD, L.o, e->d, E, T, L.o_b), 1, T);
+    return last_product(e, plain(e->b_a, H * VD, L.o, e->d, E, T, L.o_b), T);
 }
 
 // ---- state-space duality (Mamba-2) ----
@@ -951,11 +965,11 @@ int mix_ssd(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &cx) {
         GemmArgs o = plain(e->b_sdy, inner, L.o, e->d, E, T);
         o.a_norm_w = L.gn; o.a_eps = e->eps; o.a_parts = L.parts;
         if (L.parts == 1) o.a_parts = 0;          // one part: the plain instance's whole-row norm
-        return gemm(e, o, 1, T);
+        return last_product(e, o, T);
     }
     GroupNormArgs oa{e->b_sdy, L.gn, e->b_a, T, inner, L.parts, e->eps};
     if ((r = launch<GroupNormArgs>(e, k_group_norm, dim3(T * L.parts), dim3(small ? 1024 : 128), 0, oa))) return r;
-    return gemm(e, plain(e->b_a, inner, L.o, e->d, E, T), 1, T);
+    return last_product(e, plain(e->b_a, inner, L.o, e->d, E, T), T);
 }
 
 int mix(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &cx) {
@@ -995,7 +1009,7 @@ int ff_glu_dense(LayeredEngine *e, const Layer &L, uint32_t T) {
         GluArgs ga{e->b_f, 2 * L.ff, e->b_f2, L.ff, nullptr, T, L.ff, 0u};
         if ((r = launch<GluArgs>(e, k_glu, dim3(ew_grid((size_t)T * L.ff)), dim3(256), 0, ga))) return r;
     }
-    return gemm(e, plain(e->b_f2, L.ff, L.down, e->d, e->E, T), 1, T);
+    return last_product(e, plain(e->b_f2, L.ff, L.down, e->d, e->E, T), T);
 }
 
 // experts chosen by sigmoid scores: e->h2 -> the rows of e->b_eo (one per token and choice, in expert order) and, with a shared expert,
@@ -1067,12 +1081,24 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const
         if (e->form == FORM_SANDWICH && e->norm_kind == NORM_DYT) {
             // the same two updates through Dynamic-Tanh norms; e->hm already holds norm1(x) (from the embedding or the update before)
             const Dyt *next_d1 = ri + 1 < e->runs.size() ? &e->layers[e->runs[ri + 1].layer].d1 : nullptr;
-            if ((r = mix(e, L, run, cx))) return r;
-            if (L.has_mlp) {
-                if ((r = dyt_residual(e, nullptr, L.d1b, &L.d2, e->h2, nullptr, T))) return r;
-                const bool moe = L.ff_kind == FF_MOE_SCORED;
-                if ((r = moe ? ff_moe_scored(e, L, T) : ff_glu_dense(e, L, T)) || (r = dyt_residual(e, moe ? &L : nullptr, L.d2b, next_d1, e->hm, keep, T))) return r;
-            } else if ((r = dyt_residual(e, nullptr, L.d1b, next_d1, e->hm, keep, T))) return r;
+            // short portions: a residual update is the epilogue of the product before it (the norms are elementwise), except after routed experts
+            const bool ride = T <= kGemvMaxM;
+            const Dyt *after_mix = L.has_mlp ? &L.d2 : next_d1;
+            e->res.on = ride; e->res.post = L.d1b; e->res.pre = after_mix ? *after_mix : Dyt{};
+            e->res.out = after_mix ? (L.has_mlp ? e->h2 : e->hm) : nullptr; e->res.keep = L.has_mlp ? nullptr : keep;
+            r = mix(e, L, run, cx);
+            e->res.on = false;
+            if (r) return r;
+            if (!ride && (r = dyt_residual(e, nullptr, L.d1b, after_mix, L.has_mlp ? e->h2 : e->hm, L.has_mlp ? nullptr : keep, T))) return r;
+            if (L.has_mlp && L.ff_kind == FF_MOE_SCORED) {
+                if ((r = ff_moe_scored(e, L, T)) || (r = dyt_residual(e, &L, L.d2b, next_d1, e->hm, keep, T))) return r;
+            } else if (L.has_mlp) {
+                e->res.on = ride; e->res.post = L.d2b; e->res.pre = next_d1 ? *next_d1 : Dyt{}; e->res.out = next_d1 ? e->hm : nullptr; e->res.keep = keep;
+                r = ff_glu_dense(e, L, T);
+                e->res.on = false;
+                if (r) return r;
+                if (!ride && (r = dyt_residual(e, nullptr, L.d2b, next_d1, e->hm, keep, T))) return r;
+            }
             continue;
         }
         if (e->form == FORM_SANDWICH) {

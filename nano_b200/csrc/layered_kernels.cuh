@@ -76,6 +76,11 @@ struct GemmArgs {
     // k_gemv only.  Prologue (with a_norm_w): a_parts > 1 norms row r of A in a_parts equal parts, each by its own root mean square
     // (K / a_parts columns each, a multiple of 8; at most 32 parts).
     uint32_t a_parts;
+    // k_gemv only (instances EXT 4 and 5).  Residual epilogue of a sublayer's last product, for designs whose norms are elementwise
+    // (Dynamic Tanh, tanh(alpha u) w + b): instead of storing C, column n of row r updates the residual stream in place,
+    // x[r][n] += tanh(res_pa v) res_pw[n] + res_pb[n], keeps a copy (res_keep, optional) and writes the next sublayer's input
+    // res_out[r][n] = tanh(res_na x[r][n]) res_nw[n] + res_nb[n] (res_out optional).  Rows of x, res_out and res_keep are N long.
+    float *res_x, *res_out, *res_keep; const float *res_pw, *res_pb, *res_nw, *res_nb; float res_pa, res_na;
 };
 
 // Programmatic dependent launch: every kernel first lets the NEXT kernel of its stream be scheduled (its blocks then sit in their own
@@ -407,7 +412,7 @@ __device__ __forceinline__ void warp_dots(const WT *wr, const float *(&ap)[kGemv
 }
 
 // EXT 1: the instance that also knows the convolution-range epilogue, EXT 2: the PolyNorm prologue, EXT 3: the gated pair, EXT 4: the
-// norm in equal parts (registers the plain one keeps)
+// norm in equal parts, EXT 5: the plain product with the residual epilogue, which EXT 4 knows too (registers the plain one keeps)
 template <typename WT, int EXT = 0>
 __device__ __forceinline__ void gemv_body(const GemmArgs &a, float *red) {
     const GroupView gv = group_view(a, blockIdx.y);
@@ -502,7 +507,16 @@ __device__ __forceinline__ void gemv_body(const GemmArgs &a, float *red) {
         }
 #pragma unroll
         for (uint32_t i = 0; i < kGemvMaxM; i++)
-            if (i < rows) store_c(a, a.C + (size_t)(gv.r0 + i) * a.ldc + gv.c0 + n, epilogue(acc[i], a, gv.bias, n));
+            if (i < rows) {
+                const float v = epilogue(acc[i], a, gv.bias, n);
+                if ((EXT == 4 || EXT == 5) && a.res_x) {
+                    const size_t at = (size_t)(gv.r0 + i) * a.N + n;
+                    const float xv = a.res_x[at] + fmaf(tanhf(a.res_pa * v), a.res_pw[n], a.res_pb[n]);
+                    a.res_x[at] = xv;
+                    if (a.res_keep) a.res_keep[at] = xv;
+                    if (a.res_out) a.res_out[at] = fmaf(tanhf(a.res_na * xv), a.res_nw[n], a.res_nb[n]);
+                } else store_c(a, a.C + (size_t)(gv.r0 + i) * a.ldc + gv.c0 + n, v);
+            }
     }
 }
 
