@@ -5,7 +5,7 @@
 // families and dispatches through that table; each family lives in translation units of its own and is reached through ONE weak
 // creation symbol, so a library linked without a family still loads and answers "not part of this build" for its models:
 //     nb_family_nano_create     engine.cu    BD4SURLM model-file images (Nano / Qwen2 / Qwen3 decoders, F32 / Q80 / Q4K)
-//     nb_family_layered_create  layered.cu   config.json + model.safetensors folders whose config lists its layers (Famudra, Rakarax)
+//     nb_family_layered_create  layered.cu   config.json + model.safetensors folders whose config lists its layers (Famudra, Rakarax, Gokinex)
 #pragma once
 #include <stdint.h>
 
