@@ -1591,6 +1591,8 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
             if ((r = ld.stacked({"bigram"}, {(uint64_t)e->buckets + 1u}, E, &e->pairs))) return r;
         }
         if ((r = load_dyt(ld, "embed.norm", E, &e->embed_norm)) || (r = load_dyt(ld, "final.norm", E, &e->final_dyt))) return r;
+        // positions a sequence can reach: every page the state manager will own (the position tables cover them all)
+        const uint32_t page_tokens = ((max_tokens + kPage - 1) / kPage + std::max(1u, env_u32("NB200_MAX_SEQS", 8))) * kPage;
         for (uint32_t i = 0; i < NL; i++) {
             Run q; q.layer = i; e->runs.push_back(q);
             const nb::Json &lj = layers->arr[i];
@@ -1599,7 +1601,7 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
             const nb::Json *type = lj.get("type"), *mixer = lj.get("mixer");
             if (!type || type->t != nb::Json::Str || !mixer || mixer->t != nb::Json::Obj) return fail(NB200_EINVAL, "layer %u needs \"type\" and \"mixer\"", i);
             if ((r = load_dyt(ld, p + "norm1", E, &L.d1)) || (r = load_dyt(ld, p + "norm1b", E, &L.d1b))) return r;
-            if (type->str == "attention") { L.type = MIX_DIFF_ATTN; r = load_diff_attn(ld, mixer, p + "mix.", &L, E, max_tokens, e->layers, i); }
+            if (type->str == "attention") { L.type = MIX_DIFF_ATTN; r = load_diff_attn(ld, mixer, p + "mix.", &L, E, page_tokens, e->layers, i); }
             else if (type->str == "mamba2") { L.type = MIX_SSD; r = load_ssd(ld, mixer, p + "mix.", &L, E); }
             else return fail(NB200_EINVAL, "layer %u: mixer type \"%s\" is not known", i, type->str.c_str());
             if (r) return r;
@@ -1819,8 +1821,9 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
     CK(cudaMemset(e->dpos, 0, 64)); CK(cudaMemset(e->zero_dev, 0, 64));
     e->graphs.assign(e->max_seqs, nullptr);
     DM(e->b_xn, (size_t)kWantBatch * E * 4); DM(e->logits, (size_t)kWantBatch * e->V * 4);
-    DM(e->ids_dev, ((size_t)max_tokens + 16) * 4); DM(e->want_dev, kWantBatch * 4); DM(e->next_dev, 64); DM(e->seen, e->V);
-    CK(cudaMemset(e->ids_dev, 0, ((size_t)max_tokens + 16) * 4));
+    const size_t n_ids = (size_t)e->n_pages * kPage + 16;          // a single-token step stores its token at the sequence's position: every position the pages can hold
+    DM(e->ids_dev, n_ids * 4); DM(e->want_dev, kWantBatch * 4); DM(e->next_dev, 64); DM(e->seen, e->V);
+    CK(cudaMemset(e->ids_dev, 0, n_ids * 4));
     CK(cudaMemset(e->seen, 0, e->V));
     if (env_u32("NB200_KEEP_RESIDUALS", 0)) DM(e->keep, e->runs.size() * T * E * 4);
     CK(cudaHostAlloc(&e->tok_host, 64, cudaHostAllocDefault));

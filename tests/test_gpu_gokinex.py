@@ -398,6 +398,27 @@ def test_greedy_generation(tmp_path):
     assert [int(x) for x in p.stdout.split()] == [int(x) for x in ids[:total]]
 
 
+def test_sampled_generation_and_penalty(tmp_path):
+    """The device sampler and the repetition penalty on the implicit sequence, whose slot also carries the previous token."""
+    cfg = mixed_cfg(vocab=80)
+    eng, w = build(tmp_path, cfg)
+    prompt = [5, 17, 3, 44]
+    ids = np.zeros(32, np.uint32); ids[:4] = prompt
+    for pos in range(3):
+        eng.next_greedy(ids, pos, 1)
+    tok, top6 = eng.next_sampled(ids, 3, 1.0, 0.8, 0.95, 0.01)
+    ref = O.forward(cfg, w, prompt, np.float64)[-1]
+    assert top6[0] == int(np.argmax(ref)) and tok == top6[0]          # a coin near 0 takes the most probable token
+    eng.forward(5, 0); eng.forward(17, 1)                             # position 0 starts over: the pair row is the first token's again
+    assert rel(eng.logits()[None, :], O.forward(cfg, w, [5, 17], np.float64)[-1:]) < F32_TOL
+    pen = O.forward(cfg, w, [5, 17, 3], np.float64)[-1].copy()
+    for i in (5, 17):
+        pen[i] = pen[i] / 50.0 if pen[i] > 0 else pen[i] * 50.0
+    ids[:3] = [5, 17, 3]
+    assert eng.next_greedy(ids, 2, 0, 50.0) == int(np.argmax(pen))
+    eng.close()
+
+
 def test_bad_folders_are_refused(tmp_path):
     cfg = md.gokinex_config(30, 32, [("attention", att(kv_from=0), None)])
     with pytest.raises(E.NB200Error):          # kv_from names itself
