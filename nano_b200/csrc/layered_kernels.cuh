@@ -1002,7 +1002,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, attn_two_blocks(RCH, QT, EXAC
 // One block per token: router logits z_e = W_router[e] . h in fp32 (a warp per expert, lanes stride over the width), then the
 // `top` largest (ties: the lower expert index first) and their weights = softmax over the chosen logits only; counts[e] += 1 per
 // choice.  Dynamic shared memory: route_smem(NE, threads) bytes.
-// mode 0: weights = softmax over the chosen logits; mode 1: weights = sigmoid of the chosen logits, as they are (not renormalised).
+// mode 0: weights = softmax over the chosen logits; mode 1: weights = sigmoid of the chosen logits, taken as they are (they need not sum to 1).
 // extra: the router matrix carries that many more rows after the experts'; their logits go to extra_out [T][extra] and take no part
 // in the choice (a gate of a shared expert, computed with the router's precision).  wrow (optional): the weights once more in
 // expert-sorted row order, wrow[slot[t][j]] = wt[t][j], for a product that scales its rows.

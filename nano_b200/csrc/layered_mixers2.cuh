@@ -5,7 +5,7 @@
 //
 //   embedding            k_embed_pair (token row x scale + a hashed row for the (previous, current) token pair; the previous token
 //                        lives in the sequence's state slot)
-//   norms                Dyt (Dynamic Tanh: tanh(alpha u) w + b, no mean and no variance), k_dyt_residual (x += dyt(sublayer output),
+//   norms                Dyt (Dynamic Tanh: tanh(alpha u) w + b, purely elementwise), k_dyt_residual (x += dyt(sublayer output),
 //                        where the output may be a mixer's, a dense feed-forward's or the sum of routed experts and a gated shared
 //                        expert; the next sublayer's input norm of the updated x in the same pass), k_final_dyt
 //   rotary positions     k_rope_kv (interleaved pairs (2i, 2i+1) over the first `dims` coordinates of every map of every head, angles

@@ -16,7 +16,7 @@ import numpy as np
 
 
 def dyt(u, t, name):
-    """Dynamic Tanh: no mean, no variance."""
+    """Dynamic Tanh: elementwise, nothing is averaged."""
     return np.tanh(float(t[name + ".alpha"]) * u) * t[name] + t[name + ".b"]
 
 
