@@ -39,7 +39,7 @@ def _newer(target: str, sources) -> bool:
 UNITS = {
     "api.cu": ["family.h", "modeldir.h", "../../include/nano_b200.h"],
     "modeldir.cu": ["modeldir.h"],
-    "layered.cu": ["layered_kernels.cuh", "layered_mixers.cuh", "layered_mixers2.cuh", "family.h", "modeldir.h", "sample_host.h", "../../include/nano_b200.h"],
+    "layered.cu": ["layered_kernels.cuh", "layered_mixers.cuh", "layered_mixers2.cuh", "layered_mixers3.cuh", "family.h", "modeldir.h", "sample_host.h", "../../include/nano_b200.h"],
     "engine.cu": ["kernels.cuh", "expf_ref.cuh", "stream_args.h", "stream_host.h", "sample_host.h", "family.h", "../../include/nano_b200.h"],
     "stream.cu": ["kernels.cuh", "expf_ref.cuh", "stream_args.h", "stream_host.h", "stream.cuh"],
     "sample.cu": ["kernels.cuh", "expf_ref.cuh", "sample_host.h"],

@@ -41,6 +41,7 @@ const DirFamily kDirFamilies[] = {
     {"Famudra", nb_family_layered_create, "layered.cu"},
     {"Rakarax", nb_family_layered_create, "layered.cu"},
     {"Gokinex", nb_family_layered_create, "layered.cu"},
+    {"Vumunex", nb_family_layered_create, "layered.cu"},
 };
 }  // namespace
 

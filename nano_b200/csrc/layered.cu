@@ -12,6 +12,14 @@
 // head over the same values, rotary positions on interleaved pairs with frequencies rescaled by wavelength, optionally on another
 // layer's keys and values) and "mamba2" (state-space duality with a scalar decay per head and token); feed-forward "dense" (gated
 // gelu) or "moe" (silu experts chosen by sigmoid scores that weight the expert's input, plus a shared expert behind a sigmoid gate).
+// "Vumunex" -- pre-norm sequential sublayers over `streams` copies of the residual (hyper-connections: a sublayer reads a weighted sum
+// of the streams through a bias-free layer norm and its output, times a per-channel layer scale and one multiplier for the whole model,
+// returns into every stream while a small matrix mixes the streams); the token row times a fixed scale; mixers "latent_attention"
+// (direct queries against an RMS-normed key/value latent, no positions, a sliding window, a softmax with one learned extra term per
+// head in its denominator, a sigmoid output gate) and "latent_attention_2" (the same latent with a rotated key part shared by the heads
+// beside it, rotary positions on interleaved pairs, causal, ordinary softmax, output gate); feed-forward "dense" (exact gelu) or "moe"
+// (clamped gated experts chosen by their softmax scores, weighted on the way out, plus a shared expert); "loop" as below, without
+// the embedding added again.
 // "Famudra" -- parallel layers  x <- x + (mixer(shift(norm1 x)) + ff(norm2 x))  with scalar-gain RMS norms and a
 // token shift on the mixer input; mixers "rglru" (gelu branch x conv + real-gated linear recurrent unit) and "latent_attention"
 // (queries and keys/values through normed low-rank latents, no positions, causal softmax); feed-forward "moe" (top-k routed
@@ -45,6 +53,7 @@
 #include "layered_kernels.cuh"
 #include "layered_mixers.cuh"
 #include "layered_mixers2.cuh"
+#include "layered_mixers3.cuh"
 #include "modeldir.h"
 #include "sample_host.h"
 
@@ -60,8 +69,9 @@ struct Weight { void *p = nullptr; uint32_t rows = 0, cols = 0; };
 enum MixerType { MIX_RGLRU = 0, MIX_LATENT_ATTN = 1, MIX_RETENTION = 2, MIX_WINDOW_SSM = 3, MIX_DIFF_ATTN = 4, MIX_SSD = 5 };
 // how a layer combines its sublayers: Famudra's parallel form with a token shift and scalar-gain norms, or sequential sublayers
 // between an input norm and an output norm each (vector gains stored around zero)
-enum LayerForm { FORM_PARALLEL_SHIFT = 0, FORM_SANDWICH = 1 };
-enum FfKind { FF_NONE = 0, FF_MOE = 1, FF_DENSE_POLY = 2, FF_DENSE_GLU = 3, FF_MOE_SCORED = 4 };
+// or pre-norm sublayers over hyper-connected residual streams (bias-free layer norms)
+enum LayerForm { FORM_PARALLEL_SHIFT = 0, FORM_SANDWICH = 1, FORM_HYPER = 2 };
+enum FfKind { FF_NONE = 0, FF_MOE = 1, FF_DENSE_POLY = 2, FF_DENSE_GLU = 3, FF_MOE_SCORED = 4, FF_DENSE_GELU = 5 };
 // the norms of the sequential form: unit RMS times a vector gain stored around zero, or Dynamic Tanh
 enum NormKind { NORM_RMS_ZERO = 0, NORM_DYT = 1 };
 
@@ -76,6 +86,12 @@ struct Layer {
     uint32_t H = 0, dim = 0, vdim = 0, R = 0, QR = 0; float scale = 0.0f;
     Weight dqkv, uq, ukT, uv;
     float *dq_norm = nullptr, *dkv_norm = nullptr;
+    // latent attention with direct queries (QR == 0): proj = [q | down-projection | gate]; RD rotated key columns beside the latent
+    // (rot_dims of them turn, table rot_tab), RS the length of a cache row, window (kAttnNoWindow: causal), sink per head (optional),
+    // has_gate: sigmoid(W_g h) multiplies the concatenated heads
+    uint32_t RD = 0, RS = 0; float *sink = nullptr; bool has_gate = false;
+    // hyper-connected form: layer norms of the two sublayers, their layer scales (optional) and connection weights [in | out | mix]
+    float *ln1 = nullptr, *ln2 = nullptr, *ls1 = nullptr, *ls2 = nullptr, *hc1 = nullptr, *hc2 = nullptr;
     // sandwich form: input / output norms of the mixer and of the feed-forward
     float *n1 = nullptr, *n1b = nullptr, *n2 = nullptr, *n2b = nullptr;
     // retention: proj = [q | k | v | g]
@@ -100,6 +116,9 @@ struct Layer {
     // feed-forward
     int ff_kind = FF_NONE; float *act = nullptr;
     bool has_mlp = false, has_shared = false;
+    // scored experts: how the router weighs (k_route's mode), whether the weight scales what the expert reads (else its output), whether
+    // the shared expert sits behind a gate row of the router, the gated unit (k_gemv's glu) and its limits
+    uint32_t route_mode = 1, glu_kind = 2; bool score_in = true, sh_gate = false; float limit = 0.0f, slimit = 0.0f;
     uint32_t NE = 0, top = 0, ff = 0, sff = 0;
     float *router = nullptr;
     Weight up, down, sup, sdown;
@@ -149,6 +168,7 @@ struct LayeredEngine : nb::EngineBase {
     float *b_dpart = nullptr, *b_sseg = nullptr, *b_sdx = nullptr, *b_sdy = nullptr, *b_f2 = nullptr, *b_hg = nullptr, *b_sh2 = nullptr, *b_sg = nullptr, *b_wrow = nullptr; uint32_t *b_dtick = nullptr;
     uint32_t *ids_dev = nullptr, *want_dev = nullptr, *next_dev = nullptr, *tok_host = nullptr; uint8_t *seen = nullptr;
     uint32_t last_T = 0;
+    uint32_t S = 1; float res_mult = 1.0f; float *xs = nullptr;      // hyper-connected form: streams, the model's residual multiplier, the streams [S][chunk][E]
     uint32_t *dpos = nullptr, *zero_dev = nullptr;            // device-side position of a captured decode step; a constant 0
     bool branch_streams = true;      // a layer's feed-forward and shared expert on streams of their own (NB200_NO_BRANCH_STREAMS=1: one stream)
     bool use_pdl = true; bool use_graph = true; std::vector<cudaGraphExec_t> graphs; uint32_t graph_launches = 0;
@@ -277,7 +297,7 @@ int load_latent_attn(Loader &ld, const nb::Json *m, const std::string &p, Layer 
     if (!u32_of(m, "heads", &L->H) || !u32_of(m, "dim", &L->dim) || !u32_of(m, "vdim", &L->vdim) || !u32_of(m, "kv_rank", &L->R) || !u32_of(m, "q_rank", &L->QR) ||
         !m->number("scale", &sc))
         return fail(NB200_EINVAL, "%s: a latent_attention mixer needs heads, dim, vdim, kv_rank, q_rank and scale", p.c_str());
-    L->scale = (float)sc;
+    L->scale = (float)sc; L->RS = L->R; L->window = kAttnNoWindow;
     if (!L->H || !L->dim || !L->vdim || !L->R || !L->QR) return fail(NB200_EINVAL, "%s: zero-sized attention", p.c_str());
     if (L->R > 512) return fail(NB200_EINVAL, "%s: kv_rank %u above 512 has no attention kernel", p.c_str(), L->R);
     const uint64_t H = L->H, D = L->dim, VD = L->vdim, R = L->R, QR = L->QR;
@@ -539,7 +559,9 @@ int load_glu_dense(Loader &ld, const nb::Json *f, const std::string &p, Layer *L
 }
 
 // mixture of gated silu experts chosen by sigmoid scores; the router matrix carries the shared expert's gate as one more row
-int load_moe_scored(Loader &ld, const nb::Json *f, const std::string &p, Layer *L, uint32_t E) {
+// clamped: the experts are clamped gated units with expert.limit / shared.limit, chosen by softmax scores over all experts that weigh
+// their OUTPUT, and the shared expert has no gate
+int load_moe_scored(Loader &ld, const nb::Json *f, const std::string &p, Layer *L, uint32_t E, bool clamped = false) {
     if (!u32_of(f->get("router"), "experts", &L->NE) || !u32_of(f->get("router"), "top", &L->top) || !u32_of(f->get("expert"), "ff", &L->ff))
         return fail(NB200_EINVAL, "%s: a moe feed-forward needs router.experts, router.top and expert.ff", p.c_str());
     if (!L->NE || !L->top || L->top > L->NE || !L->ff) return fail(NB200_EINVAL, "%s: experts %u / top %u / ff %u unusable", p.c_str(), L->NE, L->top, L->ff);
@@ -547,12 +569,17 @@ int load_moe_scored(Loader &ld, const nb::Json *f, const std::string &p, Layer *
     int r;
     if (f->present("shared")) {
         if (!u32_of(f->get("shared"), "ff", &L->sff) || !L->sff) return fail(NB200_EINVAL, "%s: shared.ff missing", p.c_str());
-        L->has_shared = true;
+        L->has_shared = true; L->sh_gate = !clamped;
         if ((r = ld.stacked({p + "shared.gate", p + "shared.up"}, {L->sff, L->sff}, E, &L->sup)) || (r = ld.stacked({p + "shared.down"}, {E}, L->sff, &L->sdown))) return r;
+    }
+    if (clamped) {
+        double lim = 0.0, slim = 0.0;
+        if (!f->get("expert")->number("limit", &lim) || (L->has_shared && !f->get("shared")->number("limit", &slim))) return fail(NB200_EINVAL, "%s: clamped experts need expert.limit (and shared.limit)", p.c_str());
+        L->limit = (float)lim; L->slimit = (float)slim; L->route_mode = 2; L->glu_kind = 3; L->score_in = false;
     }
     {
         std::vector<float> all;
-        if ((r = append_rows(ld, p + "router", L->NE, E, 0, L->NE, &all)) || (L->has_shared && (r = append_rows(ld, p + "shared.sg", 1, E, 0, 1, &all))) || (r = ld.put_f32(all, &L->router))) return r;
+        if ((r = append_rows(ld, p + "router", L->NE, E, 0, L->NE, &all)) || (L->sh_gate && (r = append_rows(ld, p + "shared.sg", 1, E, 0, 1, &all))) || (r = ld.put_f32(all, &L->router))) return r;
     }
     std::vector<std::string> ups, downs; std::vector<uint64_t> ur, dr;
     for (uint32_t i = 0; i < L->NE; i++) {
@@ -562,6 +589,70 @@ int load_moe_scored(Loader &ld, const nb::Json *f, const std::string &p, Layer *
     }
     if ((r = ld.stacked(ups, ur, E, &L->up)) || (r = ld.stacked(downs, dr, L->ff, &L->down))) return r;
     return 0;
+}
+
+// latent attention with direct queries: q = W_q h laid out per head as [dim | rot_dim]; the down-projection gives the latent (kv_rank
+// rows, RMS-normed with a vector gain) and rot_dim more rows, one rotated key part for all heads.  Optional by presence: rot_dim / rot,
+// mask.size (sliding window), the tensor sink (one more term in the softmax denominator per head), the tensor g (sigmoid output gate).
+int load_latent_attn_direct(Loader &ld, const nb::Json *m, const std::string &p, Layer *L, uint32_t E, uint32_t positions) {
+    double sc;
+    if (!u32_of(m, "heads", &L->H) || !u32_of(m, "dim", &L->dim) || !u32_of(m, "vdim", &L->vdim) || !u32_of(m, "kv_rank", &L->R) || !m->number("scale", &sc))
+        return fail(NB200_EINVAL, "%s: a latent attention mixer needs heads, dim, vdim, kv_rank and scale", p.c_str());
+    L->scale = (float)sc; L->QR = 0;
+    if (m->present("rot_dim") && !u32_of(m, "rot_dim", &L->RD)) return fail(NB200_EINVAL, "%s: rot_dim must be a non-negative integer", p.c_str());
+    if (!L->H || !L->dim || !L->vdim || !L->R) return fail(NB200_EINVAL, "%s: zero-sized attention", p.c_str());
+    if (L->R > 512) return fail(NB200_EINVAL, "%s: kv_rank %u above 512 has no attention kernel", p.c_str(), L->R);
+    int r;
+    if (L->RD && m->present("rot")) {
+        const nb::Json *rot = m->get("rot");
+        if (!u32_of(rot, "dims", &L->rot_dims) || L->rot_dims > L->RD || (L->rot_dims & 1u)) return fail(NB200_EINVAL, "%s: rot needs an even dims <= rot_dim", p.c_str());
+        if (L->rot_dims && (r = rope_table(ld, rot, p, L->rot_dims, positions, &L->rot_tab))) return r;
+    }
+    L->window = kAttnNoWindow;
+    if (m->present("mask")) {
+        if (!u32_of(m->get("mask"), "size", &L->window) || !L->window) return fail(NB200_EINVAL, "%s: mask.size must be a positive integer", p.c_str());
+        L->window = std::min(L->window, kAttnNoWindow);
+    }
+    const uint64_t H = L->H, D = L->dim, VD = L->vdim, R = L->R, RD = L->RD;
+    L->RS = (uint32_t)((R + RD + 3u) & ~(uint64_t)3u);
+    L->has_gate = ld.dir->tensors.count(p + "g") != 0;
+    if (L->has_gate) r = ld.stacked({p + "q", p + "dkv", p + "g"}, {H * (D + RD), R + RD, H * VD}, E, &L->proj);
+    else r = ld.stacked({p + "q", p + "dkv"}, {H * (D + RD), R + RD}, E, &L->proj);
+    if (r || (r = ld.vec(p + "dkv.norm", {R}, &L->dkv_norm)) || (r = ld.stacked({p + "uv"}, {H * VD}, R, &L->uv)) || (r = ld.stacked({p + "o"}, {E}, H * VD, &L->o))) return r;
+    if (ld.dir->tensors.count(p + "sink") && (r = ld.vec(p + "sink", {H}, &L->sink))) return r;
+    std::vector<float> uk, t(H * R * D); std::vector<uint64_t> s;
+    if ((r = ld.host_f32(p + "uk", &uk, &s)) || (r = ld.expect(p + "uk", s, {H * D, R}))) return r;
+    for (uint64_t h = 0; h < H; h++)          // [H*dim, R] -> per head [R, dim]: absorbed query = q_h W_uk,h
+        for (uint64_t dd = 0; dd < D; dd++)
+            for (uint64_t k = 0; k < R; k++) t[(h * R + k) * D + dd] = uk[(h * D + dd) * R + k];
+    return ld.put_w(t, (uint32_t)(H * R), (uint32_t)D, &L->ukT);
+}
+
+// dense feed-forward down(gelu(up h)) with the exact (erf) gelu
+int load_dense_gelu(Loader &ld, const nb::Json *f, const std::string &p, Layer *L, uint32_t E) {
+    if (!u32_of(f, "ff", &L->ff) || !L->ff) return fail(NB200_EINVAL, "%s: a dense feed-forward needs ff", p.c_str());
+    L->has_mlp = true; L->ff_kind = FF_DENSE_GELU;
+    int r;
+    if ((r = ld.stacked({p + "up"}, {L->ff}, E, &L->up))) return r;
+    return ld.stacked({p + "down"}, {E}, L->ff, &L->down);
+}
+
+// connection weights of one sublayer, packed [in S | out S | mix S x S (from, to)]; without the tensors a single stream is the plain residual
+int load_hc(Loader &ld, const std::string &p, uint32_t S, float **dst) {
+    std::vector<float> all;
+    if (!ld.dir->tensors.count(p + "in")) {
+        if (S != 1) return fail(NB200_EINVAL, "%s: %u residual streams need the tensors %sin, %sout and %smix", p.c_str(), S, p.c_str(), p.c_str(), p.c_str());
+        all = {1.0f, 1.0f, 1.0f};
+        return ld.put_f32(all, dst);
+    }
+    std::vector<float> h; std::vector<uint64_t> sh; int r;
+    if ((r = ld.host_f32(p + "in", &h, &sh)) || (r = ld.expect(p + "in", sh, {S}))) return r;
+    all.insert(all.end(), h.begin(), h.end());
+    if ((r = ld.host_f32(p + "out", &h, &sh)) || (r = ld.expect(p + "out", sh, {S}))) return r;
+    all.insert(all.end(), h.begin(), h.end());
+    if ((r = ld.host_f32(p + "mix", &h, &sh)) || (r = ld.expect(p + "mix", sh, {S, S}))) return r;
+    all.insert(all.end(), h.begin(), h.end());
+    return ld.put_f32(all, dst);
 }
 
 // ---------------- launches ----------------
@@ -623,12 +714,14 @@ size_t attn_smem(uint32_t R, int qt) { return ((size_t)qt * kAttnWarps * R + (si
 
 template <int RCH, int QT>
 int attn_launch_r(LayeredEngine *e, const AttnArgs &a, dim3 grid, dim3 block, size_t smem) {
+    if (a.KX || a.window < kAttnNoWindow || a.sink)      // the instance with the options
+        return a.R == (uint32_t)RCH * 32u ? launch<AttnArgs>(e, k_latent_attn<RCH, QT, true, true>, grid, block, smem, a) : launch<AttnArgs>(e, k_latent_attn<RCH, QT, false, true>, grid, block, smem, a);
     return a.R == (uint32_t)RCH * 32u ? launch<AttnArgs>(e, k_latent_attn<RCH, QT, true>, grid, block, smem, a) : launch<AttnArgs>(e, k_latent_attn<RCH, QT, false>, grid, block, smem, a);
 }
 template <int QT>
 int attn_launch_qt(LayeredEngine *e, const AttnArgs &a, uint32_t rch) {
     const dim3 grid((a.T + QT - 1) / QT, a.nsplit, (a.H + kAttnWarps - 1) / kAttnWarps), block(kAttnWarps * 32);
-    const size_t smem = attn_smem(a.R, QT);
+    const size_t smem = attn_smem(a.R + a.KX, QT);
     if (rch <= 2) return attn_launch_r<2, QT>(e, a, grid, block, smem);
     if (rch <= 4) return attn_launch_r<4, QT>(e, a, grid, block, smem);
     if (rch <= 8) return attn_launch_r<8, QT>(e, a, grid, block, smem);
@@ -642,6 +735,8 @@ template <int RCH, int QT>
 int attn_optin_r(int smem) {
     CK(cudaFuncSetAttribute((const void *)k_latent_attn<RCH, QT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     CK(cudaFuncSetAttribute((const void *)k_latent_attn<RCH, QT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    CK(cudaFuncSetAttribute((const void *)k_latent_attn<RCH, QT, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    CK(cudaFuncSetAttribute((const void *)k_latent_attn<RCH, QT, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     return 0;
 }
 template <int QT>
@@ -684,32 +779,50 @@ int mix_rglru(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &cx) {
 
 int mix_latent_attn(LayeredEngine *e, const Layer &L, const Run &run, const Ctx &cx) {
     const uint32_t E = e->E, T = cx.T, pos0 = cx.pos0; const uint32_t *table = cx.table, *pos_ptr = cx.pos_ptr; int r;
-    const uint32_t H = L.H, R = L.R, QR = L.QR;
-    if ((r = gemm(e, plain(e->hm, E, L.dqkv, e->b_z, QR + R, T), 1, T))) return r;
-    LatentNormArgs na{e->b_z, QR + R, L.dq_norm, L.dkv_norm, e->b_cq, run.cache, table, QR, R, pos0, e->eps, pos_ptr};
-    if (T <= kGemvMaxM) {      // the norms ride on the query up-projection
-        GemvLatentArgs ga{plain(e->b_z, QR + R, L.uq, e->b_q, H * L.dim, T), na, T};
-        ga.g.a_norm_w = L.dq_norm; ga.g.a_eps = e->eps; ga.g.round_a = e->f32 ? 0u : 1u;
-        const dim3 grid(gemv_blocks(e, ga.g.N, 1)), block(256);
-        if ((r = e->f32 ? launch<GemvLatentArgs>(e, k_gemv_latent<float>, grid, block, 0, ga) : launch<GemvLatentArgs>(e, k_gemv_latent<__nv_bfloat16>, grid, block, 0, ga))) return r;
+    const uint32_t H = L.H, R = L.R, QR = L.QR, RS = L.RS;
+    GemmArgs g{};      // absorb: qa[t][h][0..R) = q[t][h] W_uk,h
+    g.W = L.ukT.p; g.ldw = L.dim; g.C = e->b_qa; g.ldc = H * RS; g.M = T; g.N = R; g.K = L.dim;
+    g.a_gmod = H; g.c_gcols = RS; g.w_gstride = (uint64_t)R * L.dim;
+    const uint32_t QW = H * (L.dim + L.RD), ZW = R + L.RD, P = QW + ZW + (L.has_gate ? H * L.vdim : 0u);      // direct queries: columns of the joint product
+    if (QR) {      // queries through a normed latent of their own
+        if ((r = gemm(e, plain(e->hm, E, L.dqkv, e->b_z, QR + R, T), 1, T))) return r;
+        LatentNormArgs na{e->b_z, QR + R, L.dq_norm, L.dkv_norm, e->b_cq, run.cache, table, QR, R, pos0, e->eps, pos_ptr};
+        if (T <= kGemvMaxM) {      // the norms ride on the query up-projection
+            GemvLatentArgs ga{plain(e->b_z, QR + R, L.uq, e->b_q, H * L.dim, T), na, T};
+            ga.g.a_norm_w = L.dq_norm; ga.g.a_eps = e->eps; ga.g.round_a = e->f32 ? 0u : 1u;
+            const dim3 grid(gemv_blocks(e, ga.g.N, 1)), block(256);
+            if ((r = e->f32 ? launch<GemvLatentArgs>(e, k_gemv_latent<float>, grid, block, 0, ga) : launch<GemvLatentArgs>(e, k_gemv_latent<__nv_bfloat16>, grid, block, 0, ga))) return r;
+        } else {
+            if ((r = launch<LatentNormArgs>(e, k_latent_norm, dim3(T), dim3(128), 0, na))) return r;
+            if ((r = gemm(e, plain(e->b_cq, QR, L.uq, e->b_q, H * L.dim, T), 1, T))) return r;
+        }
+        g.A = e->b_q; g.lda = H * L.dim; g.a_gcols = L.dim;
+        if ((r = gemm(e, g, H, T))) return r;
     } else {
-        if ((r = launch<LatentNormArgs>(e, k_latent_norm, dim3(T), dim3(128), 0, na))) return r;
-        if ((r = gemm(e, plain(e->b_cq, QR, L.uq, e->b_q, H * L.dim, T), 1, T))) return r;
+        // one product gives [q | down-projection | gate]; the latent's norm, both rotations and the cache write are one kernel, for
+        // short portions the last block of the absorb product
+        if ((r = gemm(e, plain(e->hm, E, L.proj, e->b_z, P, T, nullptr, L.has_gate ? EPI_SIGMOID_TAIL : EPI_NONE, QW + ZW), 1, T))) return r;
+        LatentRopeArgs ra{e->b_z, P, 0u, QW, L.dkv_norm, run.cache, table, e->b_qa, T, H, L.dim, L.RD, R, RS, L.rot_dims, L.rot_tab, pos0, e->eps, pos_ptr};
+        g.A = e->b_z; g.lda = P; g.a_gcols = L.dim + L.RD;
+        if (T <= kGemvMaxM) {
+            GemvLatentRopeArgs ga{g, ra};
+            ga.g.round_a = e->f32 ? 0u : 1u;
+            const dim3 grid(gemv_blocks(e, g.N, H), H), block(256);
+            if ((r = e->f32 ? launch<GemvLatentRopeArgs>(e, k_gemv_latent_rope<float>, grid, block, 0, ga) : launch<GemvLatentRopeArgs>(e, k_gemv_latent_rope<__nv_bfloat16>, grid, block, 0, ga))) return r;
+        } else if ((r = launch<LatentRopeArgs>(e, k_latent_rope, dim3(T), dim3(128), 0, ra)) || (r = gemm(e, g, H, T))) return r;
     }
-    GemmArgs g{};      // absorb: qa[t][h] = q[t][h] W_uk,h  -> [R]
-    g.A = e->b_q; g.lda = H * L.dim; g.W = L.ukT.p; g.ldw = L.dim; g.C = e->b_qa; g.ldc = H * R; g.M = T; g.N = R; g.K = L.dim;
-    g.a_gmod = H; g.a_gcols = L.dim; g.c_gcols = R; g.w_gstride = (uint64_t)R * L.dim;
-    if ((r = gemm(e, g, H, T))) return r;
-    AttnArgs aa{e->b_qa, run.cache, table, e->b_ol, e->b_part, T, H, R, pos0, 1u, L.scale, pos_ptr, e->b_tick};
-    if (pos_ptr) aa.nsplit = kSplitMax;           // the position is not known here: splits without keys write empty partials
-    else if (T <= kGemvMaxM) {
-        const uint32_t tiles = (pos0 + T + kPage - 1) / kPage;
-        aa.nsplit = std::max(1u, std::min(kSplitMax, tiles / 2u));
+    AttnArgs aa{e->b_qa, run.cache, table, e->b_ol, e->b_part, T, H, R, pos0, 1u, L.scale, pos_ptr, e->b_tick, RS - R, L.window, L.sink};
+    if (T <= kGemvMaxM) {      // short portions: the key pages in sight are dealt out to several blocks (two pages each at least)
+        // a captured step does not know the position: the most pages a window can span; splits without keys write empty partials
+        const uint32_t reach = pos_ptr ? e->max_tokens : pos0 + T;
+        const uint32_t pages = (std::min(reach, L.window + T) + kPage - 1) / kPage;
+        aa.nsplit = std::max(1u, std::min(kSplitMax, pages / 2u));
     }
     if ((r = attn_launch(e, aa, (R + 31) / 32))) return r;
-    GemmArgs v{};      // values: ov[t][h] = W_uv,h ol[t][h]
+    GemmArgs v{};      // values: ov[t][h] = W_uv,h ol[t][h], times the output gate where the design has one
     v.A = e->b_ol; v.lda = H * R; v.W = L.uv.p; v.ldw = R; v.C = e->b_ov; v.ldc = H * L.vdim; v.M = T; v.N = L.vdim; v.K = R;
     v.a_gmod = H; v.a_gcols = R; v.c_gcols = L.vdim; v.w_gstride = (uint64_t)L.vdim * R;
+    if (!QR && L.has_gate) { v.mul = e->b_z + QW + ZW; v.ldm = P; }
     if ((r = gemm(e, v, H, T))) return r;
     if ((r = gemm(e, plain(e->b_ov, H * L.vdim, L.o, e->d, E, T), 1, T))) return r;
     return 0;
@@ -1016,21 +1129,22 @@ int ff_glu_dense(LayeredEngine *e, const Layer &L, uint32_t T) {
 // e->b_so and the gate logits e->b_sg; the residual kernel adds them up.  The score weights the expert's INPUT; the experts have no
 // bias, so act(s g) (s u) of the unweighted products g, u is the same number.  The shared expert runs on a second stream.
 int ff_moe_scored(LayeredEngine *e, const Layer &L, uint32_t T) {
-    const uint32_t E = e->E, NL = L.NE + (L.has_shared ? 1u : 0u);
+    const uint32_t E = e->E, NL = L.NE + (L.sh_gate ? 1u : 0u);
     const bool small = T <= kGemvMaxM;
     int r;
     if (L.has_shared && e->branch_streams) CK(cudaEventRecord(e->ev_fork, e->stream));
-    RouteArgs ra{e->h2, L.router, e->b_idx, e->b_wt, e->b_cnt, e->b_off, e->b_fill, e->b_slot, e->b_rows, T, L.NE, L.top, E, 1u, L.has_shared ? 1u : 0u, e->b_sg, e->b_wrow};
+    float *wrow = L.score_in ? e->b_wrow : nullptr;
+    RouteArgs ra{e->h2, L.router, e->b_idx, e->b_wt, e->b_cnt, e->b_off, e->b_fill, e->b_slot, e->b_rows, T, L.NE, L.top, E, L.route_mode, L.sh_gate ? 1u : 0u, e->b_sg, wrow};
     if (small) { if ((r = launch<RouteArgs>(e, k_route_small, dim3(1), dim3(1024), route_smem(NL, 1024), ra))) return r; }
     else if ((r = launch<RouteArgs>(e, k_route, dim3(T), dim3(256), route_smem(NL, 256), ra)) || (r = launch<RouteArgs>(e, k_route_place, dim3(1), dim3(1024), 0, ra))) return r;
     GemmArgs u{};
     u.A = e->h2; u.lda = E; u.W = L.up.p; u.ldw = E; u.M = T; u.K = E; u.a_gmod = 1;
     u.g_off = e->b_off; u.a_rows = e->b_rows; u.w_gstride = (uint64_t)2 * L.ff * E;
-    if (small) { u.C = e->b_hb; u.ldc = L.ff; u.N = L.ff; u.glu = 2u; u.row_scale = e->b_wrow; }
+    if (small) { u.C = e->b_hb; u.ldc = L.ff; u.N = L.ff; u.glu = L.glu_kind; u.glu_limit = L.limit; u.row_scale = wrow; }
     else { u.C = e->b_hg; u.ldc = 2 * L.ff; u.N = 2 * L.ff; }
     if ((r = gemm(e, u, L.NE, T, false, T * L.top))) return r;
     if (!small) {
-        GluArgs ga{e->b_hg, 2 * L.ff, e->b_hb, L.ff, e->b_wrow, T * L.top, L.ff, 1u};
+        GluArgs ga{e->b_hg, 2 * L.ff, e->b_hb, L.ff, wrow, T * L.top, L.ff, L.glu_kind == 3u ? 2u : 1u, L.limit};
         if ((r = launch<GluArgs>(e, k_glu, dim3(ew_grid((size_t)T * L.top * L.ff)), dim3(256), 0, ga))) return r;
     }
     GemmArgs dn{};
@@ -1041,11 +1155,11 @@ int ff_moe_scored(LayeredEngine *e, const Layer &L, uint32_t T) {
     if (e->branch_streams) { e->cur = e->side; CK(cudaStreamWaitEvent(e->side, e->ev_fork, 0)); }
     if (small) {
         GemmArgs su = plain(e->h2, E, L.sup, e->b_sh2, L.sff, T);
-        su.N = L.sff; su.glu = 2u;
+        su.N = L.sff; su.glu = L.glu_kind; su.glu_limit = L.slimit;
         if ((r = gemm(e, su, 1, T))) return r;
     } else {
         if ((r = gemm(e, plain(e->h2, E, L.sup, e->b_sh, 2 * L.sff, T), 1, T))) return r;
-        GluArgs ga{e->b_sh, 2 * L.sff, e->b_sh2, L.sff, nullptr, T, L.sff, 1u};
+        GluArgs ga{e->b_sh, 2 * L.sff, e->b_sh2, L.sff, nullptr, T, L.sff, L.glu_kind == 3u ? 2u : 1u, L.slimit};
         if ((r = launch<GluArgs>(e, k_glu, dim3(ew_grid((size_t)T * L.sff)), dim3(256), 0, ga))) return r;
     }
     if ((r = gemm(e, plain(e->b_sh2, L.sff, L.sdown, e->b_so, E, T), 1, T))) return r;
@@ -1058,6 +1172,33 @@ int dyt_residual(LayeredEngine *e, const Layer *moe, const Dyt &post, const Dyt 
     DytResArgs a{e->x, moe ? nullptr : e->d, moe ? e->b_eo : nullptr, e->b_slot, moe ? moe->top : 0u, moe && moe->has_shared ? e->b_so : nullptr, e->b_sg,
                  post, pre ? *pre : Dyt{}, pre ? out : nullptr, keep, T, e->E};
     return launch<DytResArgs>(e, k_dyt_residual, dim3(ew_grid((size_t)T * e->E)), dim3(256), 0, a);
+}
+
+// dense feed-forward with the exact gelu as the first product's epilogue: e->h2 -> e->d
+int ff_dense_gelu(LayeredEngine *e, const Layer &L, uint32_t T) {
+    int r;
+    if ((r = gemm(e, plain(e->h2, e->E, L.up, e->b_f, L.ff, T, nullptr, EPI_GELU_ERF), 1, T))) return r;
+    return gemm(e, plain(e->b_f, L.ff, L.down, e->d, e->E, T), 1, T);
+}
+
+// hyper-connected residual streams: the update after a sublayer (hc, ls: its connection weights and layer scale; moe: its output is the
+// chosen experts' rows) and the input norm of the sublayer that follows (next_hc's `in` weights, gain next_w, into out); with tokens
+// the streams are filled from the embedding instead
+int hc_step(LayeredEngine *e, const float *hc, const float *ls, const Layer *moe, const float *next_hc, const float *next_w, float *out, float *keep, uint32_t T,
+            const uint32_t *tok_dev = nullptr, const uint32_t *pos_ptr = nullptr) {
+    HcArgs a{};
+    a.xs = e->xs; a.s_stride = (size_t)e->chunk_cap * e->E; a.S = e->S;
+    if (!tok_dev) {
+        if (moe) { a.eo = e->b_eo; a.slot = e->b_slot; a.wt = e->b_wt; a.top = moe->top; a.shared = moe->has_shared ? e->b_so : nullptr; }
+        else a.y = e->d;
+    }
+    a.ls = ls; a.hc = hc; a.mult = e->res_mult;
+    a.next_in = next_hc; a.next_w = next_w; a.out = next_hc ? out : nullptr; a.keep = keep;
+    a.T = T; a.E = e->E; a.eps = e->eps;
+    a.tokens = tok_dev; a.pos_ptr = pos_ptr; a.embed = e->embed.p; a.emb_scale = e->emb_scale;
+    // a short portion is a few lone blocks: wide ones, so that a thread's chain of loads stays short
+    const dim3 block(T <= kGemvMaxM && e->E >= 2048 ? 1024 : (T <= kGemvMaxM && e->E >= 1024 ? 512 : 256));
+    return e->f32 ? launch<HcArgs>(e, k_hc_step<float>, dim3(T), block, 0, a) : launch<HcArgs>(e, k_hc_step<__nv_bfloat16>, dim3(T), block, 0, a);
 }
 
 int sandwich(LayeredEngine *e, const float *d, const float *w_post, const float *w_pre, float *out, float *keep, uint32_t T, const float *d2 = nullptr) {
@@ -1078,6 +1219,18 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const
         const Run &run = e->runs[ri];
         const Layer &L = e->layers[run.layer];
         float *keep = e->keep ? e->keep + ri * (size_t)e->chunk_cap * E : nullptr;
+        if (e->form == FORM_HYPER) {
+            // e->hm already holds the mixer's input (from the embedding step or the update before); every update also prepares the
+            // input of the sublayer that follows (this layer's feed-forward, or the next run's mixer)
+            const Layer *NX = ri + 1 < e->runs.size() ? &e->layers[e->runs[ri + 1].layer] : nullptr;
+            if ((r = mix(e, L, run, cx))) return r;
+            if (!L.has_mlp) { if ((r = hc_step(e, L.hc1, L.ls1, nullptr, NX ? NX->hc1 : nullptr, NX ? NX->ln1 : nullptr, e->hm, keep, T))) return r; continue; }
+            if ((r = hc_step(e, L.hc1, L.ls1, nullptr, L.hc2, L.ln2, e->h2, nullptr, T))) return r;
+            const bool moe = L.ff_kind == FF_MOE_SCORED;
+            if ((r = moe ? ff_moe_scored(e, L, T) : ff_dense_gelu(e, L, T))) return r;
+            if ((r = hc_step(e, L.hc2, L.ls2, moe ? &L : nullptr, NX ? NX->hc1 : nullptr, NX ? NX->ln1 : nullptr, e->hm, keep, T))) return r;
+            continue;
+        }
         if (e->form == FORM_SANDWICH && e->norm_kind == NORM_DYT) {
             // the same two updates through Dynamic-Tanh norms; e->hm already holds norm1(x) (from the embedding or the update before)
             const Dyt *next_d1 = ri + 1 < e->runs.size() ? &e->layers[e->runs[ri + 1].layer].d1 : nullptr;
@@ -1154,6 +1307,11 @@ int run_layers(LayeredEngine *e, uint32_t slot, uint32_t T, uint32_t pos0, const
 }
 
 int embed_tokens(LayeredEngine *e, uint32_t slot, const uint32_t *tok_dev, uint32_t T, const uint32_t *pos_ptr = nullptr, uint32_t pos0 = 0) {
+    if (e->form == FORM_HYPER) {      // token row x scale into every stream, and the first sublayer's input norm
+        e->cur = e->stream;
+        const Layer &L0 = e->layers[e->runs[0].layer];
+        return hc_step(e, nullptr, nullptr, nullptr, L0.hc1, L0.ln1, e->hm, nullptr, T, tok_dev, pos_ptr);
+    }
     if (e->norm_kind == NORM_DYT) {      // token row x scale + pair row, the stack's input norm, and the first sublayer's input norm
         e->cur = e->stream;
         EmbedPairArgs a{tok_dev, pos_ptr, e->embed.p, e->pairs.p, e->x, e->hm, reinterpret_cast<uint32_t *>(e->state + (size_t)slot * e->slot_floats + e->st_tok),
@@ -1177,6 +1335,12 @@ int embed_tokens(LayeredEngine *e, uint32_t slot, const uint32_t *tok_dev, uint3
 
 // logits of `nw` rows of the current chunk (want_dev holds their indices) -> e->logits [nw][V]
 int head_rows(LayeredEngine *e, uint32_t nw, const uint32_t *want_dev = nullptr) {
+    if (e->form == FORM_HYPER) {
+        k_final_ln<<<nw, 256, 0, e->stream>>>(e->xs, (size_t)e->chunk_cap * e->E, e->S, want_dev ? want_dev : e->want_dev, e->final_norm, e->b_xn, e->E, e->eps);
+        CK(cudaGetLastError());
+        e->launches++;
+        return gemm(e, plain(e->b_xn, e->E, e->head, e->logits, e->V, nw), 1, nw);
+    }
     if (e->norm_kind == NORM_DYT) {
         k_final_dyt<<<nw, 256, 0, e->stream>>>(e->x, want_dev ? want_dev : e->want_dev, e->final_dyt, e->b_xn, e->E);
         CK(cudaGetLastError());
@@ -1573,7 +1737,7 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
     int r;
     const nb::Json *arch = cfg.get("architecture");
     const std::string design = arch && arch->t == nb::Json::Str ? arch->str : "";
-    e->form = design == "Rakarax" || design == "Gokinex" ? FORM_SANDWICH : FORM_PARALLEL_SHIFT;
+    e->form = design == "Rakarax" || design == "Gokinex" ? FORM_SANDWICH : (design == "Vumunex" ? FORM_HYPER : FORM_PARALLEL_SHIFT);
     e->norm_kind = design == "Gokinex" ? NORM_DYT : NORM_RMS_ZERO;
     if ((r = ld.stacked({"embed"}, {e->V}, E, &e->embed)) || (r = ld.stacked({"head"}, {e->V}, E, &e->head))) return r;
     e->layers.resize(NL);
@@ -1610,6 +1774,37 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
                 if ((r = load_dyt(ld, p + "norm2", E, &L.d2)) || (r = load_dyt(ld, p + "norm2b", E, &L.d2b))) return r;
                 if (kind && kind->t == nb::Json::Str && kind->str == "dense") r = load_glu_dense(ld, f, p + "mlp.", &L, E);
                 else if (kind && kind->t == nb::Json::Str && kind->str == "moe") r = load_moe_scored(ld, f, p + "mlp.", &L, E);
+                else return fail(NB200_EINVAL, "layer %u: feed-forward kind \"%s\" is not known", i, kind && kind->t == nb::Json::Str ? kind->str.c_str() : "?");
+                if (r) return r;
+            }
+        }
+    } else if (e->form == FORM_HYPER) {
+        const nb::Json *emb = cfg.get("embedding");
+        double sc = 1.0, mult = 1.0;
+        if (emb && emb->t == nb::Json::Obj && emb->present("scale") && !emb->number("scale", &sc)) return fail(NB200_EINVAL, "embedding.scale must be a number");
+        if (cfg.present("residual_mult") && !cfg.number("residual_mult", &mult)) return fail(NB200_EINVAL, "residual_mult must be a number");
+        e->emb_scale = (float)sc; e->res_mult = (float)mult;
+        if (cfg.present("streams") && (!u32_of(&cfg, "streams", &e->S) || !e->S || e->S > kMaxStreams)) return fail(NB200_EINVAL, "streams must be between 1 and %u", kMaxStreams);
+        if ((r = ld.vec("final.norm", {E}, &e->final_norm))) return r;
+        const uint32_t page_tokens = ((max_tokens + kPage - 1) / kPage + std::max(1u, env_u32("NB200_MAX_SEQS", 8))) * kPage;      // every position the cache pages can hold
+        for (uint32_t i = 0; i < NL; i++) {
+            const nb::Json &lj = layers->arr[i];
+            Layer &L = e->layers[i];
+            const std::string p = "l" + std::to_string(i) + ".";
+            const nb::Json *type = lj.get("type"), *mixer = lj.get("mixer");
+            if (!type || type->t != nb::Json::Str || !mixer || mixer->t != nb::Json::Obj) return fail(NB200_EINVAL, "layer %u needs \"type\" and \"mixer\"", i);
+            if ((r = ld.vec(p + "norm1", {E}, &L.ln1)) || (r = load_hc(ld, p + "hc1.", e->S, &L.hc1))) return r;
+            if (dir->tensors.count(p + "ls1") && (r = ld.vec(p + "ls1", {E}, &L.ls1))) return r;
+            // both kinds are one mechanism: what a kind has (rotated part, window, sink, gate) shows in its config entry and tensors
+            if (type->str == "latent_attention" || type->str == "latent_attention_2") { L.type = MIX_LATENT_ATTN; r = load_latent_attn_direct(ld, mixer, p + "mix.", &L, E, page_tokens); }
+            else return fail(NB200_EINVAL, "layer %u: mixer type \"%s\" is not known", i, type->str.c_str());
+            if (r) return r;
+            if (lj.present("mlp")) {
+                const nb::Json *f = lj.get("mlp"), *kind = f->get("kind");
+                if ((r = ld.vec(p + "norm2", {E}, &L.ln2)) || (r = load_hc(ld, p + "hc2.", e->S, &L.hc2))) return r;
+                if (dir->tensors.count(p + "ls2") && (r = ld.vec(p + "ls2", {E}, &L.ls2))) return r;
+                if (kind && kind->t == nb::Json::Str && kind->str == "dense") r = load_dense_gelu(ld, f, p + "mlp.", &L, E);
+                else if (kind && kind->t == nb::Json::Str && kind->str == "moe") r = load_moe_scored(ld, f, p + "mlp.", &L, E, true);
                 else return fail(NB200_EINVAL, "layer %u: feed-forward kind \"%s\" is not known", i, kind && kind->t == nb::Json::Str ? kind->str.c_str() : "?");
                 if (r) return r;
             }
@@ -1665,14 +1860,16 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
                 if ((r = ld.vec(p + "norm2", {}, &L.norm2)) || (r = load_moe(ld, lj.get("mlp"), p + "mlp.", &L, E))) return r;
             }
         }
-        // order of the layer runs
+    }
+    if (e->form == FORM_PARALLEL_SHIFT || e->form == FORM_HYPER) {
+        // order of the layer runs: a span may run several times in a row (the parallel form adds the embedding output again before every pass but the first)
         uint32_t lo = 0, hi = 0, times = 1;
         if (cfg.present("loop")) {
             const nb::Json *lp = cfg.get("loop");
             if (!u32_of(lp, "start", &lo) || !u32_of(lp, "stop", &hi) || !u32_of(lp, "times", &times) || lo > hi || hi > NL || times < 1) return fail(NB200_EINVAL, "loop needs 0 <= start <= stop <= layers and times >= 1");
         }
         for (uint32_t i = 0; i < lo; i++) { Run q; q.layer = i; e->runs.push_back(q); }
-        for (uint32_t p = 0; p < times; p++) for (uint32_t i = lo; i < hi; i++) { Run q; q.layer = i; q.add_embed = p > 0 && i == lo; e->runs.push_back(q); if (q.add_embed) e->keep_x0 = true; }
+        for (uint32_t p = 0; p < times; p++) for (uint32_t i = lo; i < hi; i++) { Run q; q.layer = i; q.add_embed = e->form == FORM_PARALLEL_SHIFT && p > 0 && i == lo; e->runs.push_back(q); if (q.add_embed) e->keep_x0 = true; }
         for (uint32_t i = hi; i < NL; i++) { Run q; q.layer = i; e->runs.push_back(q); }
     }
 
@@ -1697,7 +1894,10 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
                 q.st_S = off; off += (size_t)L.H * L.vdim * L.mN;
                 break;
             case MIX_RGLRU: q.st_S = off; off += L.C; q.st_conv = off; off += (size_t)(L.taps - 1) * L.C; break;
-            case MIX_LATENT_ATTN: DM(q.cache, (size_t)e->n_pages * kPage * L.R * 4); break;
+            case MIX_LATENT_ATTN:      // rows of [latent | rotated key part | padding]
+                DM(q.cache, (size_t)e->n_pages * kPage * L.RS * 4);
+                CK(cudaMemset(q.cache, 0, (size_t)e->n_pages * kPage * L.RS * 4));
+                break;
             case MIX_RETENTION: q.st_S = off; off += (size_t)L.H * L.vdim * L.dim; break;
             default:          // window attention + selective scan: the tails of both convolutions, the scan state, a cache of key/value rows
                 q.st_conv = off; off += (size_t)(L.a_taps - 1) * (L.H + L.G) * L.dim;
@@ -1732,7 +1932,7 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
             size_t &sm = win_smem[L.dim <= 32 ? 0 : L.dim <= 64 ? 1 : L.dim <= 128 ? 2 : 3];
             sm = std::max(sm, std::max(win_attn_smem(L.H, L.dim, L.RL, qt), win_attn_smem(L.H, L.dim, L.RL, 1)));
         }
-        if (L.ff_kind == FF_DENSE_POLY) sF = std::max(sF, L.ff);
+        if (L.ff_kind == FF_DENSE_POLY || L.ff_kind == FF_DENSE_GELU) sF = std::max(sF, L.ff);
         if (L.type == MIX_DIFF_ATTN) {
             sP = std::max(sP, L.H * 2 * L.dim + (L.kv_from < 0 ? L.G * (2 * L.dim + L.vdim) : 0u)); sA = std::max(sA, L.H * L.vdim);
             sDP = std::max(sDP, L.H * 2 * (L.vdim + 2)); sDT = std::max(sDT, (L.H + L.a_hpb1 - 1) / L.a_hpb1);
@@ -1788,17 +1988,21 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
     uint32_t mFF2 = 0, mSFF2 = 0;      // scored experts: [gate | up] rows of a prefill portion
     for (const Layer &L : e->layers) {
         if (L.type == MIX_RGLRU) mC = std::max(mC, L.C);
-        else if (L.type == MIX_LATENT_ATTN) { mZ = std::max(mZ, L.QR + L.R); mQR = std::max(mQR, L.QR); mQ = std::max(mQ, L.H * L.dim); mHR = std::max(mHR, L.H * L.R); mOV = std::max(mOV, L.H * L.vdim); }
+        else if (L.type == MIX_LATENT_ATTN) {
+            mZ = std::max(mZ, L.QR ? L.QR + L.R : L.H * (L.dim + L.RD + L.vdim) + L.R + L.RD); mQR = std::max(mQR, L.QR); mQ = std::max(mQ, L.H * L.dim);
+            mHR = std::max(mHR, L.H * L.RS); mOV = std::max(mOV, L.H * L.vdim);
+        }
         if (L.ff_kind == FF_MOE || L.ff_kind == FF_MOE_SCORED) { mNE = std::max(mNE, L.NE + 1u); mTop = std::max(mTop, L.top); mFF = std::max(mFF, L.top * L.ff); mSFF = std::max(mSFF, L.sff); }
         if (L.ff_kind == FF_MOE_SCORED) { mFF2 = std::max(mFF2, 2 * L.top * L.ff); mSFF2 = std::max(mSFF2, 2 * L.sff); }
     }
+    if (e->form == FORM_HYPER) DM(e->xs, (size_t)e->S * T * E * 4);
     DM(e->x, T * E * 4); DM(e->hm, T * E * 4); DM(e->h2, T * E * 4); DM(e->d, T * E * 4);
     if (e->keep_x0) DM(e->x0, T * E * 4);
     if (mC) { DM(e->b_yx, T * 2 * mC * 4); DM(e->b_u, T * mC * 4); DM(e->b_g, T * 2 * mC * 4); DM(e->b_sy, T * mC * 4); }
     if (mZ) {
         DM(e->b_z, T * mZ * 4); DM(e->b_cq, T * mQR * 4); DM(e->b_q, T * mQ * 4); DM(e->b_qa, T * mHR * 4); DM(e->b_ol, T * mHR * 4); DM(e->b_ov, T * mOV * 4);
         uint32_t mPart = 0, mR = 0;
-        for (const Layer &L : e->layers) if (L.type == MIX_LATENT_ATTN) { mPart = std::max(mPart, L.H * (L.R + 2)); mR = std::max(mR, L.R); }
+        for (const Layer &L : e->layers) if (L.type == MIX_LATENT_ATTN) { mPart = std::max(mPart, L.H * (L.R + 2)); mR = std::max(mR, L.RS); }
         DM(e->b_part, (size_t)kGemvMaxM * kSplitMax * mPart * 4);
         uint32_t mHG = 0;
         for (const Layer &L : e->layers) if (L.type == MIX_LATENT_ATTN) mHG = std::max(mHG, (L.H + kAttnWarps - 1) / kAttnWarps);

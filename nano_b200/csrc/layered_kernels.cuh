@@ -40,7 +40,7 @@ constexpr uint32_t kAttnWarps = 8;        // heads per attention block
 constexpr uint32_t kGemvMaxM = 4;         // rows a k_gemv launch handles per group
 
 enum CMode : uint32_t { C_ADD = 1, C_SCALE = 2 };
-enum Epi : uint32_t { EPI_NONE = 0, EPI_BIAS = 1, EPI_GELU_SPLIT = 2, EPI_SIGMOID = 3, EPI_RELU2 = 4, EPI_GELU_CONV = 5, EPI_SOFTPLUS = 6, EPI_CONV_RANGES = 7 };
+enum Epi : uint32_t { EPI_NONE = 0, EPI_BIAS = 1, EPI_GELU_SPLIT = 2, EPI_SIGMOID = 3, EPI_RELU2 = 4, EPI_GELU_CONV = 5, EPI_SOFTPLUS = 6, EPI_CONV_RANGES = 7, EPI_SIGMOID_TAIL = 8, EPI_GELU_ERF = 9 };
 
 // C[r, c0 + n] = epi( sum_k A[arow(r), a0 + k] * W[g][n, k] + bias[g][n] )   for the rows r of group g
 //   rows of group g : [g_off[g], g_off[g+1])  when g_off is given (sizes known on the device only), else [0, M)
@@ -52,7 +52,7 @@ struct GemmArgs {
     uint32_t M, N, K, lda, ldw, ldc;
     uint32_t a_gmod, a_gcols, c_gcols, b_gstride;
     uint64_t w_gstride;
-    uint32_t epi, split;      // EPI_GELU_SPLIT: gelu_tanh on columns n < split, bias only on the others
+    uint32_t epi, split;      // EPI_GELU_SPLIT: gelu_tanh on columns n < split, bias only on the others; EPI_SIGMOID_TAIL: sigmoid on columns n >= split
     uint32_t round_a;         // k_gemv: round A to bf16 first (what the tensor-core kernel does to its operand)
     // k_gemv only.  Prologue: when a_norm_w is given, row r of A is used as A[r, k] / rms(A[r, 0..K)) * a_norm_w[k] (eps inside the root).
     const float *a_norm_w; float a_eps;
@@ -69,7 +69,7 @@ struct GemmArgs {
     // k_gemv only.  Epilogue EPI_CONV_RANGES: a column n inside [cr[i].n0, cr[i].n1) is channel n - n0 of causal convolution i over the
     // rows in order (no epilogue before it); every other column is stored as usual.
     struct ConvRange { uint32_t n0, n1; const float *taps, *bias; float *state, *out; uint32_t K, act; } cr[2];
-    // k_gemv only.  Gated pair (glu 1: gelu_tanh, 2: silu): W holds 2 N rows per group, [gate rows | up rows]; column n of C receives
+    // k_gemv only.  Gated pair (glu 1: gelu_tanh, 2: silu, 3: the clamped unit below): W holds 2 N rows per group, [gate rows | up rows]; column n of C receives
     // act(s g_n) (s u_n) with g_n, u_n the products of rows n and N + n and s = row_scale[row] (1 when null): a routed expert whose
     // input is weighted by the router's score, without a pass over the input.
     uint32_t glu; const float *row_scale;
@@ -81,6 +81,11 @@ struct GemmArgs {
     // x[r][n] += tanh(res_pa v) res_pw[n] + res_pb[n], keeps a copy (res_keep, optional) and writes the next sublayer's input
     // res_out[r][n] = tanh(res_na x[r][n]) res_nw[n] + res_nb[n] (res_out optional).  Rows of x, res_out and res_keep are N long.
     float *res_x, *res_out, *res_keep; const float *res_pw, *res_pb, *res_nw, *res_nb; float res_pa, res_na;
+    // After the epilogue: with mul given, the value of row r (of the output) and column c0 + n is multiplied by mul[r * ldm + c0 + n]
+    // (an output gate computed by an earlier product).
+    const float *mul; uint32_t ldm;
+    // Gated pair, glu 3: the clamped unit  g' = min(g, glu_limit), u' = clamp(u, -glu_limit, glu_limit),  g' sigmoid(1.702 g') (u' + 1).
+    float glu_limit;
 };
 
 // Programmatic dependent launch: every kernel first lets the NEXT kernel of its stream be scheduled (its blocks then sit in their own
@@ -106,6 +111,11 @@ __device__ __forceinline__ float gelu_tanh(float z) {
 }
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplusf_(float z) { return log1pf(expf(-fabsf(z))) + fmaxf(z, 0.0f); }
+// the clamped gated unit: the gate is capped from above, the linear branch on both sides and shifted by one
+__device__ __forceinline__ float clamped_glu(float g, float u, float limit) {
+    g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit);
+    return g * sigmoidf_(1.702f * g) * (u + 1.0f);
+}
 
 __device__ __forceinline__ float epilogue(float v, const GemmArgs &a, const float *bias, uint32_t n) {
     if (bias) v += bias[n];
@@ -114,9 +124,12 @@ __device__ __forceinline__ float epilogue(float v, const GemmArgs &a, const floa
         case EPI_SIGMOID: return sigmoidf_(v);
         case EPI_RELU2: { const float r = fmaxf(v, 0.0f); return r * r; }
         case EPI_SOFTPLUS: return softplusf_(v);
+        case EPI_SIGMOID_TAIL: return n >= a.split ? sigmoidf_(v) : v;
+        case EPI_GELU_ERF: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
         default: return v;
     }
 }
+__device__ __forceinline__ float gated(const GemmArgs &a, float v, uint32_t row, uint32_t col) { return a.mul ? v * a.mul[(size_t)row * a.ldm + col] : v; }
 __device__ __forceinline__ void store_c(const GemmArgs &a, float *dst, float v) {
     if (a.c_mode & C_SCALE) v *= a.c_scale;
     *dst = (a.c_mode & C_ADD) ? *dst + v : v;
@@ -187,7 +200,7 @@ __global__ void __launch_bounds__(256) k_gemm_f32(const GemmArgs a) {
 #pragma unroll
         for (uint32_t j = 0; j < 4; j++) {
             const uint32_t n = n0 + tx * 4 + j;
-            if (n < a.N) store_c(a, a.C + (size_t)(gv.r0 + r) * a.ldc + gv.c0 + n, epilogue(acc[i][j], a, gv.bias, n));
+            if (n < a.N) store_c(a, a.C + (size_t)(gv.r0 + r) * a.ldc + gv.c0 + n, gated(a, epilogue(acc[i][j], a, gv.bias, n), gv.r0 + r, gv.c0 + n));
         }
     }
 }
@@ -290,7 +303,7 @@ __global__ void __launch_bounds__(128) k_gemm_bf16(const GemmArgs a) {
 #pragma unroll
             for (uint32_t q = 0; q < 4; q++) {
                 const uint32_t r = m0 + wm + i * 16 + g + (q >> 1) * 8, n = n0 + wn + j * 8 + 2 * t + (q & 1u);
-                if (r < gv.rows && n < a.N) store_c(a, a.C + (size_t)(gv.r0 + r) * a.ldc + gv.c0 + n, epilogue(acc[i][j][q], a, gv.bias, n));
+                if (r < gv.rows && n < a.N) store_c(a, a.C + (size_t)(gv.r0 + r) * a.ldc + gv.c0 + n, gated(a, epilogue(acc[i][j][q], a, gv.bias, n), gv.r0 + r, gv.c0 + n));
             }
 }
 
@@ -486,7 +499,7 @@ __device__ __forceinline__ void gemv_body(const GemmArgs &a, float *red) {
             for (uint32_t i = 0; i < kGemvMaxM; i++)
                 if (i < rows) {
                     const float s = a.row_scale ? a.row_scale[gv.r0 + i] : 1.0f, g = acc[i] * s, u = up[i] * s;
-                    store_c(a, a.C + (size_t)(gv.r0 + i) * a.ldc + gv.c0 + n, (a.glu == 2u ? g / (1.0f + expf(-g)) : gelu_tanh(g)) * u);
+                    store_c(a, a.C + (size_t)(gv.r0 + i) * a.ldc + gv.c0 + n, a.glu == 3u ? clamped_glu(g, u, a.glu_limit) : (a.glu == 2u ? g / (1.0f + expf(-g)) : gelu_tanh(g)) * u);
                 }
             continue;
         }
@@ -515,7 +528,7 @@ __device__ __forceinline__ void gemv_body(const GemmArgs &a, float *red) {
                     a.res_x[at] = xv;
                     if (a.res_keep) a.res_keep[at] = xv;
                     if (a.res_out) a.res_out[at] = fmaf(tanhf(a.res_na * xv), a.res_nw[n], a.res_nb[n]);
-                } else store_c(a, a.C + (size_t)(gv.r0 + i) * a.ldc + gv.c0 + n, v);
+                } else store_c(a, a.C + (size_t)(gv.r0 + i) * a.ldc + gv.c0 + n, gated(a, v, gv.r0 + i, gv.c0 + n));
             }
     }
 }
@@ -796,7 +809,13 @@ struct AttnArgs {
     const float *qa; const float *cache; const uint32_t *table; float *out; float *part;
     uint32_t T, H, R, pos0, nsplit; float scale; const uint32_t *pos_ptr;
     uint32_t *tickets;      // nsplit > 1: one zeroed counter per (query tile, head group); the block that draws the last ticket merges
+    // Options (a design without them passes 0, kAttnNoWindow, null).  KX: a cache row is [R latent columns | KX more key columns] and a
+    // query row likewise; the score runs over all R + KX columns (a rotated key part shared by the heads beside the latent), the
+    // weighted sum over the R latent columns only.  window: query i sees key j only while i - j < window.  sink: one number per head
+    // that joins the softmax denominator as exp(sink_h), with no key and no value.
+    uint32_t KX, window; const float *sink;
 };
+constexpr uint32_t kAttnNoWindow = 1u << 30;
 // EXACT: the latent rank is RCH * 32 (64, 128, 256, 512): R is a compile-time constant, so row offsets are immediates, the
 // divisions of the staging loops are shifts and the column guards vanish.
 // Two blocks per SM (128 registers) where the shared memory of a prefill instance fits twice; measured faster at rank 256 with 8 queries,
@@ -804,35 +823,41 @@ struct AttnArgs {
 constexpr bool attn_two_blocks(int rch, int qt, bool exact) {
     return exact && qt > 1 && ((size_t)qt * kAttnWarps * rch * 32 + (size_t)kPage * (rch * 32 + 4)) * 4 <= 112u * 1024u;
 }
-template <int RCH, int QT, bool EXACT>
+// EXT: the instance that knows the options (extra key columns, window, sink); the plain one ignores them and keeps its registers
+template <int RCH, int QT, bool EXACT, bool EXT = false>
 __global__ void __launch_bounds__(kAttnWarps * 32, attn_two_blocks(RCH, QT, EXACT) ? 2 : 1) k_latent_attn(const AttnArgs a) {
     pdl_enter();
+    const uint32_t a_KX = EXT ? a.KX : 0u, a_window = EXT ? a.window : kAttnNoWindow;
+    const float *a_sink = EXT ? a.sink : nullptr;
     extern __shared__ __align__(16) float sm[];
     const uint32_t tq0 = blockIdx.x * QT, split = blockIdx.y, h0 = blockIdx.z * kAttnWarps;
     const uint32_t nq = min((uint32_t)QT, a.T - tq0);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, h = h0 + warp;
     const uint32_t R = EXACT ? (uint32_t)RCH * 32u : a.R;
-    const bool vec = (R % 4u) == 0;                // 16-byte shared-memory rows: (R + 4) / 4 is odd for R % 8 == 0, so 8 lanes hit 8 bank groups
-    const uint32_t LDC = vec ? R + 4u : R + 1u;
-    float *q_s = sm;                               // [QT][kAttnWarps][R]
-    float *c_s = sm + QT * kAttnWarps * R;         // [kPage][LDC]
+    const uint32_t RS = EXT ? R + a_KX : R;       // row length of the cache and of the queries (R itself, a constant, without extra key columns)
+    const bool vec = (R % 4u) == 0 && (RS % 4u) == 0;      // 16-byte shared-memory rows: (R + 4) / 4 is odd for R % 8 == 0, so 8 lanes hit 8 bank groups
+    const uint32_t LDC = vec ? RS + 4u : RS + 1u;
+    float *q_s = sm;                               // [QT][kAttnWarps][RS]
+    float *c_s = sm + QT * kAttnWarps * RS;        // [kPage][LDC]
     const uint32_t pos = a.pos0 + (a.pos_ptr ? *a.pos_ptr : 0u);
     const uint32_t nkeys = pos + tq0 + nq, tiles = (nkeys + kPage - 1u) / kPage;      // keys of the block's last query
-    const uint32_t tps = (tiles + a.nsplit - 1u) / a.nsplit;
-    const uint32_t tile_lo = split * tps, tile_hi = min(tiles, tile_lo + tps);
+    // the oldest key the block's FIRST query sees: tiles before it hold nothing for any query of the block
+    const uint32_t tile_first = EXT ? (pos + tq0 + 1u > a_window ? pos + tq0 + 1u - a_window : 0u) / kPage : 0u;
+    const uint32_t tps = (tiles - tile_first + a.nsplit - 1u) / a.nsplit;
+    const uint32_t tile_lo = tile_first + split * tps, tile_hi = min(tiles, tile_lo + tps);
     if (vec) {          // a query token's kAttnWarps heads are contiguous in qa: 16-byte copies, all of a thread's loads in flight
-        const uint32_t per = kAttnWarps * R / 4u, live = (min(a.H, h0 + kAttnWarps) - h0) * R / 4u;
+        const uint32_t per = kAttnWarps * RS / 4u, live = (min(a.H, h0 + kAttnWarps) - h0) * RS / 4u;
 #pragma unroll 4
         for (uint32_t i = threadIdx.x; i < QT * per; i += blockDim.x) {
             const uint32_t qi = i / per, rem = i % per;
             float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (qi < nq && rem < live) v = *(reinterpret_cast<const float4 *>(a.qa + ((size_t)(tq0 + qi) * a.H + h0) * R) + rem);
+            if (qi < nq && rem < live) v = *(reinterpret_cast<const float4 *>(a.qa + ((size_t)(tq0 + qi) * a.H + h0) * RS) + rem);
             reinterpret_cast<float4 *>(q_s)[i] = v;
         }
     } else {
-        for (uint32_t i = threadIdx.x; i < QT * kAttnWarps * R; i += blockDim.x) {
-            const uint32_t qi = i / (kAttnWarps * R), rem = i % (kAttnWarps * R), hh = h0 + rem / R;
-            q_s[i] = (qi < nq && hh < a.H) ? a.qa[((size_t)(tq0 + qi) * a.H + hh) * R + rem % R] : 0.0f;
+        for (uint32_t i = threadIdx.x; i < QT * kAttnWarps * RS; i += blockDim.x) {
+            const uint32_t qi = i / (kAttnWarps * RS), rem = i % (kAttnWarps * RS), hh = h0 + rem / RS;
+            q_s[i] = (qi < nq && hh < a.H) ? a.qa[((size_t)(tq0 + qi) * a.H + hh) * RS + rem % RS] : 0.0f;
         }
     }
     float m[QT], l[QT], o[QT][RCH];
@@ -844,10 +869,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32, attn_two_blocks(RCH, QT, EXAC
     }
     for (uint32_t tile = tile_lo; tile < tile_hi; tile++) {
         __syncthreads();
-        const float *src = a.cache + (size_t)a.table[tile] * kPage * R;
+        const float *src = a.cache + (size_t)a.table[tile] * kPage * RS;
         const uint32_t nk = min(kPage, nkeys - tile * kPage);
         if (vec) {
-            const uint32_t n4 = nk * R / 4u;
+            const uint32_t n4 = nk * RS / 4u;
             const float4 *src4 = reinterpret_cast<const float4 *>(src);
             for (uint32_t base = 0; base < n4; base += 8u * kAttnWarps * 32u) {
                 float4 v[8];
@@ -856,19 +881,21 @@ __global__ void __launch_bounds__(kAttnWarps * 32, attn_two_blocks(RCH, QT, EXAC
 #pragma unroll
                 for (int k = 0; k < 8; k++) {
                     const uint32_t i = base + k * kAttnWarps * 32u + threadIdx.x;
-                    if (i < n4) *reinterpret_cast<float4 *>(c_s + (i * 4u / R) * LDC + (i * 4u) % R) = v[k];
+                    if (i < n4) *reinterpret_cast<float4 *>(c_s + (i * 4u / RS) * LDC + (i * 4u) % RS) = v[k];
                 }
             }
         } else {
-            for (uint32_t i = threadIdx.x; i < nk * R; i += blockDim.x) c_s[(i / R) * LDC + i % R] = src[i];
+            for (uint32_t i = threadIdx.x; i < nk * RS; i += blockDim.x) c_s[(i / RS) * LDC + i % RS] = src[i];
         }
         __syncthreads();
         if (h >= a.H) continue;
-        uint32_t nkq[QT];               // keys of this tile each query sees (0: the tile lies after the query)
+        uint32_t nkq[QT], lokq[QT];     // keys [lokq, nkq) of this tile are the ones each query sees (nkq 0: the tile lies after the query)
 #pragma unroll
         for (int qi = 0; qi < QT; qi++) {
             const uint32_t kq = pos + tq0 + qi + 1u;
             nkq[qi] = ((uint32_t)qi < nq && kq > tile * kPage) ? min(nk, kq - tile * kPage) : 0u;
+            const uint32_t oldest = kq > a_window ? kq - a_window : 0u;
+            lokq[qi] = (EXT && oldest > tile * kPage) ? oldest - tile * kPage : 0u;
         }
         float sc[QT];
 #pragma unroll
@@ -877,28 +904,30 @@ __global__ void __launch_bounds__(kAttnWarps * 32, attn_two_blocks(RCH, QT, EXAC
         if (vec) {
             float sc4[4] = {0.0f, 0.0f, 0.0f, 0.0f};      // a single query: four independent partial sums instead of one long chain
             const float4 *c4 = reinterpret_cast<const float4 *>(cr);
-            for (uint32_t r4 = 0; r4 < R / 4u; r4++) {
+            auto score4 = [&](uint32_t r4) {
                 const float4 cv = c4[r4];
 #pragma unroll
                 for (int qi = 0; qi < QT; qi++) {
-                    const float4 qv = reinterpret_cast<const float4 *>(q_s + ((size_t)qi * kAttnWarps + warp) * R)[r4];
+                    const float4 qv = reinterpret_cast<const float4 *>(q_s + ((size_t)qi * kAttnWarps + warp) * RS)[r4];
                     if (QT == 1) { sc4[0] = fmaf(qv.x, cv.x, sc4[0]); sc4[1] = fmaf(qv.y, cv.y, sc4[1]); sc4[2] = fmaf(qv.z, cv.z, sc4[2]); sc4[3] = fmaf(qv.w, cv.w, sc4[3]); }
                     else sc[qi] = fmaf(qv.w, cv.w, fmaf(qv.z, cv.z, fmaf(qv.y, cv.y, fmaf(qv.x, cv.x, sc[qi]))));
                 }
-            }
+            };
+            for (uint32_t r4 = 0; r4 < R / 4u; r4++) score4(r4);
+            if (EXT) for (uint32_t r4 = R / 4u; r4 < RS / 4u; r4++) score4(r4);      // the extra key columns
             if (QT == 1) sc[0] = (sc4[0] + sc4[1]) + (sc4[2] + sc4[3]);
         } else {
-            for (uint32_t r = 0; r < R; r++) {
+            for (uint32_t r = 0; r < RS; r++) {
                 const float cv = cr[r];
 #pragma unroll
-                for (int qi = 0; qi < QT; qi++) sc[qi] = fmaf(q_s[((size_t)qi * kAttnWarps + warp) * R + r], cv, sc[qi]);
+                for (int qi = 0; qi < QT; qi++) sc[qi] = fmaf(q_s[((size_t)qi * kAttnWarps + warp) * RS + r], cv, sc[qi]);
             }
         }
         float p[QT];
         uint32_t nkmax = 0;
 #pragma unroll
         for (int qi = 0; qi < QT; qi++) {
-            const bool seen = lane < nkq[qi];
+            const bool seen = lane < nkq[qi] && lane >= lokq[qi];
             const float s = seen ? sc[qi] * a.scale : -INFINITY;
             float tm = s;
 #pragma unroll
@@ -936,7 +965,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32, attn_two_blocks(RCH, QT, EXAC
         if ((uint32_t)qi >= nq || h >= a.H) continue;
         const uint32_t t = tq0 + qi;
         if (a.nsplit == 1) {
-            const float inv = 1.0f / l[qi];
+            float den = l[qi], ow = 1.0f;
+            if (a_sink) {      // the sink joins the denominator, under the common maximum
+                const float sk = a_sink[h], mm = fmaxf(m[qi], sk);
+                ow = expf(m[qi] - mm); den = l[qi] * ow + expf(sk - mm);
+            }
+            const float inv = ow / den;
 #pragma unroll
             for (int c = 0; c < RCH; c++) { const uint32_t r = lane + 32u * c; if (r < R) a.out[((size_t)t * a.H + h) * R + r] = o[qi][c] * inv; }
         } else {
@@ -963,7 +997,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, attn_two_blocks(RCH, QT, EXAC
     if (!last_s || h >= a.H) return;
     __threadfence();
     const size_t stride = (size_t)a.H * (R + 2u);
-    const uint32_t nact = min(a.nsplit, (tiles + tps - 1u) / tps);      // splits that own key tiles; the others wrote nothing of weight
+    const uint32_t nact = min(a.nsplit, (tiles - tile_first + tps - 1u) / tps);      // splits that own key tiles; the others wrote nothing of weight
 #pragma unroll
     for (int qi = 0; qi < QT; qi++) {
         if ((uint32_t)qi >= nq) continue;
@@ -975,10 +1009,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32, attn_two_blocks(RCH, QT, EXAC
         float M = ms;
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+        if (a_sink) M = fmaxf(M, a_sink[h]);
         const float w = ls > 0.0f ? expf(ms - M) : 0.0f;
         float L = w * ls;
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
+        if (a_sink) L += expf(a_sink[h] - M);
         float acc[RCH];
 #pragma unroll
         for (int c = 0; c < RCH; c++) acc[c] = 0.0f;
@@ -1002,7 +1038,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32, attn_two_blocks(RCH, QT, EXAC
 // One block per token: router logits z_e = W_router[e] . h in fp32 (a warp per expert, lanes stride over the width), then the
 // `top` largest (ties: the lower expert index first) and their weights = softmax over the chosen logits only; counts[e] += 1 per
 // choice.  Dynamic shared memory: route_smem(NE, threads) bytes.
-// mode 0: weights = softmax over the chosen logits; mode 1: weights = sigmoid of the chosen logits, taken as they are (they need not sum to 1).
+// mode 0: weights = softmax over the chosen logits; mode 1: weights = sigmoid of the chosen logits, taken as they are (they need not sum to 1);
+// mode 2: scores = softmax over ALL experts, weights = the chosen experts' scores divided by their sum (+ 1e-20).
 // extra: the router matrix carries that many more rows after the experts'; their logits go to extra_out [T][extra] and take no part
 // in the choice (a gate of a shared expert, computed with the router's precision).  wrow (optional): the weights once more in
 // expert-sorted row order, wrow[slot[t][j]] = wt[t][j], for a product that scales its rows.
@@ -1046,6 +1083,11 @@ __device__ __forceinline__ void route_logits(const RouteArgs &a, uint32_t t, flo
 // one thread: the `top` largest of z (ties: the lower index first; z is consumed) and the softmax over them
 __device__ __forceinline__ void route_pick(const RouteArgs &a, uint32_t t, float *z) {
     uint32_t *idx = a.idx + (size_t)t * a.top; float *wt = a.wt + (size_t)t * a.top;
+    float zmax = -INFINITY, zden = 0.0f;
+    if (a.mode == 2u) {      // softmax over ALL experts: its maximum and denominator, before the choice consumes z
+        for (uint32_t e = 0; e < a.NE; e++) zmax = fmaxf(zmax, z[e]);
+        for (uint32_t e = 0; e < a.NE; e++) zden += expf(z[e] - zmax);
+    }
     for (uint32_t j = 0; j < a.top; j++) {
         float best = -INFINITY; uint32_t bi = 0xffffffffu;
         for (uint32_t e = 0; e < a.NE; e++) {
@@ -1057,6 +1099,12 @@ __device__ __forceinline__ void route_pick(const RouteArgs &a, uint32_t t, float
     }
     for (uint32_t k = 0; k < a.extra; k++) a.extra_out[(size_t)t * a.extra + k] = z[a.NE + k];
     if (a.mode == 1u) { for (uint32_t j = 0; j < a.top; j++) wt[j] = sigmoidf_(wt[j]); return; }
+    if (a.mode == 2u) {      // the chosen experts' scores, divided by their sum
+        float s = 0.0f;
+        for (uint32_t j = 0; j < a.top; j++) { wt[j] = expf(wt[j] - zmax) / zden; s += wt[j]; }
+        for (uint32_t j = 0; j < a.top; j++) wt[j] /= s + 1e-20f;
+        return;
+    }
     const float mx = wt[0];
     float s = 0.0f;
     for (uint32_t j = 0; j < a.top; j++) { wt[j] = expf(wt[j] - mx); s += wt[j]; }

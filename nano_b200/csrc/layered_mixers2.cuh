@@ -86,10 +86,12 @@ __global__ void __launch_bounds__(256) k_final_dyt(const float *__restrict__ x, 
     for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) out[(size_t)blockIdx.x * E + i] = dyt_of(n, xt[i], i);
 }
 
-// out[r][c] = act(s g) (s u),  g = gu[r][c], u = gu[r][F + c], s = row_scale[r] (1 when null); act 0: gelu (tanh form), 1: silu
-struct GluArgs { const float *gu; uint32_t ld; float *out; uint32_t ldo; const float *row_scale; uint32_t rows, F, act; };
-__device__ __forceinline__ float glu_of(float g, float u, float s, uint32_t act) {
+// out[r][c] = act(s g) (s u),  g = gu[r][c], u = gu[r][F + c], s = row_scale[r] (1 when null); act 0: gelu (tanh form), 1: silu,
+// 2: the clamped unit  min(g, limit) sigmoid(1.702 min(g, limit)) (clamp(u, -limit, limit) + 1)
+struct GluArgs { const float *gu; uint32_t ld; float *out; uint32_t ldo; const float *row_scale; uint32_t rows, F, act; float limit; };
+__device__ __forceinline__ float glu_of(float g, float u, float s, uint32_t act, float limit) {
     g *= s; u *= s;
+    if (act == 2u) return clamped_glu(g, u, limit);
     return (act ? siluf_(g) : gelu_tanh(g)) * u;
 }
 __global__ void __launch_bounds__(256) k_glu(const GluArgs a) {
@@ -98,7 +100,7 @@ __global__ void __launch_bounds__(256) k_glu(const GluArgs a) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const uint32_t r = (uint32_t)(i / a.F), c = (uint32_t)(i % a.F);
         const float *row = a.gu + (size_t)r * a.ld;
-        a.out[(size_t)r * a.ldo + c] = glu_of(row[c], row[a.F + c], a.row_scale ? a.row_scale[r] : 1.0f, a.act);
+        a.out[(size_t)r * a.ldo + c] = glu_of(row[c], row[a.F + c], a.row_scale ? a.row_scale[r] : 1.0f, a.act, a.limit);
     }
 }
 

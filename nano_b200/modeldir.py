@@ -1,4 +1,4 @@
-"""Model folders (config.json + model.safetensors) from the Python side: a writer, and random-weight Famudra, Rakarax and Gokinex models for
+"""Model folders (config.json + model.safetensors) from the Python side: a writer, and random-weight Famudra, Rakarax, Gokinex and Vumunex models for
 the benchmarks and tests.  The reader the engine uses is native (csrc/modeldir.cu); nothing here is on the compute path.
 
 A safetensors file is an 8-byte little-endian header length, that many bytes of JSON (name -> dtype, shape, data_offsets) and
@@ -252,4 +252,68 @@ def gokinex_random(config: dict, seed: int = 0, gain: float = 1.0) -> Dict[str, 
                 q = p + "mlp.shared."
                 t[q + "gate"] = lin(f["shared"]["ff"], E, 1.5); t[q + "up"] = lin(f["shared"]["ff"], E); t[q + "down"] = lin(E, f["shared"]["ff"])
                 t[q + "sg"] = lin(1, E, 2.0)
+    return t
+
+
+def vumunex_config(vocab: int, width: int, layers, streams=3, residual_mult=0.5, scale: float = 1.0, loop=None, eps: float = 1e-5) -> dict:
+    """layers: list of (type, mixer, mlp).
+    type "latent_attention": mixer {heads, dim, vdim, kv_rank, scale, mask: {size}}; type "latent_attention_2": mixer {heads, dim,
+    rot_dim, vdim, kv_rank, scale, rot: {dims, base}}; mlp: None, {"kind": "dense", "ff": f} or {"kind": "moe", "router": {"experts": n,
+    "top": k}, "expert": {"ff": f, "limit": l}, "shared": {"ff": s, "limit": l} (optional)}.  streams None: one plain residual stream
+    (the key is left out, and vumunex_random writes no connection tensors)."""
+    out = [{"type": kind, "mixer": json.loads(json.dumps(mixer)), "mlp": json.loads(json.dumps(mlp)) if mlp else None} for kind, mixer, mlp in layers]
+    cfg = {"architecture": "Vumunex", "vocab": vocab, "width": width, "embedding": {"scale": scale}, "norm": {"eps": eps},
+           "residual_mult": residual_mult, "layers": out}
+    if streams is not None:
+        cfg["streams"] = int(streams)
+    if loop:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+def vumunex_random(config: dict, seed: int = 0, gain: float = 1.0, layer_scale: bool = True) -> Dict[str, np.ndarray]:
+    """Random weights (bfloat16-representable fp32 arrays) for a Vumunex config: projections ~ N(0, gain^2 / fan_in)."""
+    rng = np.random.default_rng(seed)
+    E, V = config["width"], config["vocab"]
+    S = config.get("streams")
+
+    def lin(o, i, g=1.0):
+        return bf16_round((rng.standard_normal((o, i), dtype=np.float32) * (gain * g / np.sqrt(i))).astype(np.float32))
+
+    def vecn(n, lo, hi):
+        return bf16_round(rng.uniform(lo, hi, size=n).astype(np.float32))
+
+    t = {"embed": bf16_round(rng.standard_normal((V, E), dtype=np.float32)), "head": lin(V, E), "final.norm": vecn(E, 0.7, 1.3)}
+    for i, L in enumerate(config["layers"]):
+        p = f"l{i}."
+        m = L["mixer"]
+        H, D, VD, R, RD = m["heads"], m["dim"], m["vdim"], m["kv_rank"], m.get("rot_dim", 0)
+        t[p + "norm1"] = vecn(E, 0.7, 1.3)
+        t[p + "mix.q"] = lin(H * (D + RD), E, 2.0)
+        t[p + "mix.dkv"] = lin(R + RD, E, 2.0); t[p + "mix.dkv.norm"] = vecn(R, 0.7, 1.3)
+        t[p + "mix.uk"] = lin(H * D, R, 2.0); t[p + "mix.uv"] = lin(H * VD, R)
+        if L["type"] == "latent_attention":
+            t[p + "mix.sink"] = vecn(H, -1.0, 2.0)
+        t[p + "mix.g"] = lin(H * VD, E, 2.0); t[p + "mix.o"] = lin(E, H * VD)
+        subs = [1]
+        f = L.get("mlp")
+        if f:
+            subs.append(2)
+            t[p + "norm2"] = vecn(E, 0.7, 1.3)
+            if f["kind"] == "dense":
+                t[p + "mlp.up"] = lin(f["ff"], E, 1.5); t[p + "mlp.down"] = lin(E, f["ff"])
+            else:
+                t[p + "mlp.router"] = lin(f["router"]["experts"], E, 3.0)
+                for e in range(f["router"]["experts"]):
+                    q = p + f"mlp.e{e}."
+                    t[q + "gate"] = lin(f["expert"]["ff"], E, 2.0); t[q + "up"] = lin(f["expert"]["ff"], E, 2.0); t[q + "down"] = lin(E, f["expert"]["ff"])
+                if f.get("shared"):
+                    q = p + "mlp.shared."
+                    t[q + "gate"] = lin(f["shared"]["ff"], E, 2.0); t[q + "up"] = lin(f["shared"]["ff"], E, 2.0); t[q + "down"] = lin(E, f["shared"]["ff"])
+        for q in subs:
+            if layer_scale:
+                t[p + f"ls{q}"] = vecn(E, 0.5, 1.5)
+            if S is not None:
+                t[p + f"hc{q}.in"] = vecn(S, 0.2, 0.6); t[p + f"hc{q}.out"] = vecn(S, 0.5, 1.5)
+                t[p + f"hc{q}.mix"] = bf16_round((np.eye(S) * 0.9 + 0.1 * rng.standard_normal((S, S))).astype(np.float32))
     return t
