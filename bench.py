@@ -766,6 +766,88 @@ def gokinex_bench(args):
                       "clocks": clocks, "sizes": out}))
 
 
+# --------------------------------------------------------------------------------------------------
+# --design vumunex: the same two measurements for the Vumunex design (latent attention with direct queries: rotated key part + causal,
+# or sliding window + sink; exact-gelu dense and clamped-expert feed-forwards; four hyper-connected residual streams) beside the
+# closest model of the same runtime, Famudra (latent attention, routed experts with a shared expert, looped layers), at equal width
+# and depth.
+# --------------------------------------------------------------------------------------------------
+VUMUNEX_SIZES = {
+    # name: (width, layers, heads, dim, rot_dim, vdim, kv_rank, window, dense ff, experts, top, expert ff, shared ff, streams)
+    "w1024": (1024, 8, 16, 64, 32, 64, 256, 512, 3072, 16, 2, 512, 1024, 4),
+    "w2048": (2048, 8, 16, 128, 64, 128, 512, 1024, 6144, 16, 2, 1024, 2048, 4),
+}
+
+
+def vumunex_model(name):
+    from nano_b200 import modeldir as md
+    E_, L, H, D, RD, VD, R, W, ff, NE, top, eff, sff, S = VUMUNEX_SIZES[name]
+    moe = {"kind": "moe", "router": {"experts": NE, "top": top}, "expert": {"ff": eff, "limit": 7.0}, "shared": {"ff": sff, "limit": 7.0}}
+    layers = []
+    for i in range(L):
+        if i % 2 == 0:
+            layers.append(("latent_attention_2", {"heads": H, "dim": D, "rot_dim": RD, "vdim": VD, "kv_rank": R, "scale": (D + RD) ** -0.5,
+                                                  "rot": {"dims": RD, "base": 500000.0}}, {"kind": "dense", "ff": ff}))
+        else:
+            layers.append(("latent_attention", {"heads": H, "dim": D, "vdim": VD, "kv_rank": R, "scale": D ** -0.5, "mask": {"size": W}}, moe))
+    cfg = md.vumunex_config(FAMUDRA_VOCAB, E_, layers, streams=S, residual_mult=0.5, scale=float(E_) ** 0.5)
+    path = os.path.join(os.environ.get("NB200_MODEL_CACHE", "/tmp/nb200_models"), f"vumunex-{name}")
+    if not os.path.exists(os.path.join(path, "model.safetensors")):
+        md.write_model_dir(path + ".part", cfg, md.vumunex_random(cfg, 0))
+        os.replace(path + ".part", path)
+    return path, cfg
+
+
+def vumunex_decode_bytes(cfg, pos, wbytes=2):
+    """Algorithmic HBM bytes of one decoded token at position pos: every matrix once (the chosen experts only), the fp32 cache rows in
+    sight of every attention layer (latent + rotated key part; a window bounds them), the head."""
+    E_ = cfg["width"]; b = 0.0
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        H, D, VD, R, RD = m["heads"], m["dim"], m["vdim"], m["kv_rank"], m.get("rot_dim", 0)
+        seen = min(pos + 1, m["mask"]["size"]) if m.get("mask") else pos + 1
+        b += wbytes * ((H * (D + RD) + R + RD + H * VD) * E_ + H * D * R + H * VD * R + E_ * H * VD) + 4.0 * (R + RD) * seen
+        f = L.get("mlp")
+        if f and f["kind"] == "dense":
+            b += wbytes * 2 * E_ * f["ff"]
+        elif f:
+            b += 4.0 * f["router"]["experts"] * E_ + wbytes * 3 * E_ * (f["router"]["top"] * f["expert"]["ff"] + (f["shared"]["ff"] if f.get("shared") else 0))
+    return b + wbytes * cfg["vocab"] * E_
+
+
+def vumunex_flops_per_token(cfg, ctx):
+    fl = 2.0 * (vumunex_decode_bytes(cfg, 0, 1) - cfg["vocab"] * cfg["width"])
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        seen = min(ctx, m["mask"]["size"]) if m.get("mask") else ctx
+        fl += 2.0 * m["heads"] * (2 * m["kv_rank"] + m.get("rot_dim", 0)) * seen          # scores over latent + rotated part, weighted sums over the latent
+    return fl
+
+
+def vumunex_bench(args):
+    from nano_b200 import engine as E
+    hbm, hbm_src = peaks()
+    try:
+        tf = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        tf = 1590.0
+    ctx, n_dec, T = 1024, 128, 2048
+    sampler = ClockSampler(0); sampler.start()
+    out = {}
+    for name in (args.sizes.split(",") if args.sizes else sorted(VUMUNEX_SIZES)):
+        path, cfg = vumunex_model(name)
+        row = layered_modes(E, path, FAMUDRA_VOCAB, ctx, n_dec, T, args, hbm, tf, lambda pos, wb: vumunex_decode_bytes(cfg, pos, wb), lambda c: vumunex_flops_per_token(cfg, c))
+        ppath, pcfg = famudra_model(name)          # the closest model: the same runtime's Famudra at equal width and depth
+        args_bf16 = argparse.Namespace(**{**vars(args), "with_f32": False})
+        row["peer_famudra"] = layered_modes(E, ppath, FAMUDRA_VOCAB, ctx, n_dec, T, args_bf16, hbm, tf, lambda pos, wb: famudra_decode_bytes(pcfg, pos, wb), lambda c: famudra_flops_per_token(pcfg, c))["bf16"]
+        out[name] = row
+    clocks = sampler.stop()
+    print(json.dumps({"design": "vumunex", "unit": "tokens/s", "n_gpus": 1, "data": "synthetic (random weights)", "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "bf16_tflops": tf},
+                      "config": {"decode": f"greedy device loop, {n_dec} tokens after a {ctx}-token prompt, batch 1", "prefill": f"one portion of {T} tokens into an empty sequence",
+                                 "timing": "CUDA events on the engine's stream after warm-up", "l2": "fractions are against HBM although the weights of one token fit the 126 MB L2 at w1024"},
+                      "clocks": clocks, "sizes": out}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -782,7 +864,7 @@ def main():
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-stream", action="store_true", help="forbid the streaming kernel")
-    ap.add_argument("--design", default=None, choices=["famudra", "rakarax", "gokinex"], help="measure a model-folder design instead of the headline workload (its own JSON line)")
+    ap.add_argument("--design", default=None, choices=["famudra", "rakarax", "gokinex", "vumunex"], help="measure a model-folder design instead of the headline workload (its own JSON line)")
     ap.add_argument("--sizes", default=None, help="--design: comma-separated size names (default: all)")
     ap.add_argument("--with-f32", action="store_true", help="--design: also time the true-32-bit mode")
     args = ap.parse_args()
@@ -791,6 +873,9 @@ def main():
         return
     if args.design == "rakarax":
         rakarax_bench(args)
+        return
+    if args.design == "vumunex":
+        vumunex_bench(args)
         return
     if args.design == "gokinex":
         gokinex_bench(args)

@@ -111,3 +111,53 @@ def test_gokinex_oracle_is_causal_and_reads_what_it_should():
     r = O.rotate(u, {"dims": 4, "base": 100.0}, [0, 1, 5])
     z = (u[2, 1, 2] + 1j * u[2, 1, 3]) * np.exp(1j * 5 * 100.0 ** (-2.0 / 4))
     assert np.allclose([r[2, 1, 2], r[2, 1, 3]], [z.real, z.imag]) and np.array_equal(r[..., 4:], u[..., 4:]) and np.allclose(r[0], u[0])
+
+
+VUM_WIN = {"heads": 2, "dim": 8, "vdim": 6, "kv_rank": 10, "scale": 0.4, "mask": {"size": 3}}
+VUM_ROT = {"heads": 2, "dim": 6, "rot_dim": 4, "vdim": 8, "kv_rank": 10, "scale": 0.4, "rot": {"dims": 4, "base": 100.0}}
+VUM_MOE = {"kind": "moe", "router": {"experts": 3, "top": 2}, "expert": {"ff": 6, "limit": 0.8}, "shared": {"ff": 4, "limit": 0.5}}
+
+
+@pytest.mark.skipif(E.device_count() > 0, reason="box has a GPU")
+def test_vumunex_folder_reaches_the_layered_family(tmp_path):
+    cfg = md.vumunex_config(16, 8, [("latent_attention", VUM_WIN, {"kind": "dense", "ff": 12}), ("latent_attention_2", VUM_ROT, VUM_MOE)], streams=2, loop=(0, 1, 2))
+    w = md.vumunex_random(cfg)
+    assert w["l0.hc1.mix"].shape == (2, 2) and "l0.mix.sink" in w and "l1.mix.sink" not in w and w["l1.mix.dkv"].shape == (14, 8)
+    p = md.write_model_dir(str(tmp_path / "v"), cfg, w)
+    with pytest.raises(E.NB200Error, match="no CUDA device"):
+        E.Engine(p, 16)
+
+
+def test_vumunex_oracle_is_causal_windowed_and_routed():
+    """The plain restatement itself: a prefix gives the same logits; a token outside the window leaves no trace; the sink takes weight
+    away; the router's weights are the chosen scores over their sum; with one stream and unit connections the update is the plain
+    pre-norm residual."""
+    import vumunex_oracle as O
+    cfg = md.vumunex_config(20, 16, [("latent_attention", VUM_WIN, None)], streams=None, residual_mult=0.5)
+    w = md.vumunex_random(cfg, 3)
+    t = np.random.default_rng(0).integers(0, 20, 24)
+    full = O.forward(cfg, w, t)
+    assert np.allclose(O.forward(cfg, w, t[:10]), full[:10], atol=1e-12)
+    t2 = t.copy(); t2[5] = (t2[5] + 1) % 20
+    other = O.forward(cfg, w, t2)
+    assert np.abs(other[7] - full[7]).max() > 1e-6 and np.allclose(other[8:], full[8:], atol=1e-12)      # window 3: positions 5, 6, 7 see token 5
+    tt = {k: np.asarray(v, np.float64) for k, v in w.items()}
+    x = tt["embed"][t]
+    h = O.layer_norm(x, tt["l0.norm1"], 1e-5)
+    assert np.allclose(h.mean(-1) / tt["l0.norm1"].mean(), 0.0, atol=1.0)      # the mean is taken off before the gain
+    y = O.latent_attention(VUM_WIN, tt, "l0.mix.", h, 1e-5) * tt["l0.ls1"]
+    res = []
+    O.forward(cfg, w, t, res)
+    assert np.allclose(res[0], x + 0.5 * y, atol=1e-12)
+    hot = dict(tt); hot["l0.mix.sink"] = tt["l0.mix.sink"] + 50.0
+    assert np.abs(O.latent_attention(VUM_WIN, hot, "l0.mix.", h, 1e-5)).max() < 1e-12 * np.abs(y).max() + 1e-15
+    f = {"router": {"experts": 5, "top": 2}}
+    tr = {"r.router": np.random.default_rng(1).standard_normal((5, 16))}
+    idx, wt = O.router(f, tr, "r.", h)
+    z = h @ tr["r.router"].T
+    s = np.exp(z) / np.exp(z).sum(-1, keepdims=True)
+    assert np.array_equal(idx[:, 0], s.argmax(-1)) and np.allclose(wt.sum(-1), 1.0)
+    assert np.allclose(wt[:, 0], s.max(-1) / np.take_along_axis(s, idx, -1).sum(-1))
+    g = np.array([[3.0, -3.0]])
+    e = O.expert({"e.gate": np.eye(2), "e.up": np.eye(2), "e.down": np.eye(2)}, "e.", g, 1.0)
+    assert np.allclose(e, [[1.0 * O.sigmoid(1.702) * 2.0, -3.0 * O.sigmoid(-3.0 * 1.702) * 0.0]])      # the gate is capped from above only, the other branch on both sides
