@@ -816,7 +816,7 @@ int mix_latent_attn(LayeredEngine *e, const Layer &L, const Run &run, const Ctx 
         // a captured step does not know the position: the most pages a window can span; splits without keys write empty partials
         const uint32_t reach = pos_ptr ? e->max_tokens : pos0 + T;
         const uint32_t pages = (std::min(reach, L.window + T) + kPage - 1) / kPage;
-        aa.nsplit = std::max(1u, std::min(kSplitMax, pages / 2u));
+        aa.nsplit = std::max(1u, std::min(kSplitMax, pos_ptr ? (pages + 2u) / 2u : pages / 2u));      // a window that starts inside a page spans one page more
     }
     if ((r = attn_launch(e, aa, (R + 31) / 32))) return r;
     GemmArgs v{};      // values: ov[t][h] = W_uv,h ol[t][h], times the output gate where the design has one
@@ -1198,7 +1198,12 @@ int hc_step(LayeredEngine *e, const float *hc, const float *ls, const Layer *moe
     a.tokens = tok_dev; a.pos_ptr = pos_ptr; a.embed = e->embed.p; a.emb_scale = e->emb_scale;
     // a short portion is a few lone blocks: wide ones, so that a thread's chain of loads stays short
     const dim3 block(T <= kGemvMaxM && e->E >= 2048 ? 1024 : (T <= kGemvMaxM && e->E >= 1024 ? 512 : 256));
-    return e->f32 ? launch<HcArgs>(e, k_hc_step<float>, dim3(T), block, 0, a) : launch<HcArgs>(e, k_hc_step<__nv_bfloat16>, dim3(T), block, 0, a);
+#define HC_LAUNCH(SC) (e->f32 ? launch<HcArgs>(e, k_hc_step<float, SC>, dim3(T), block, 0, a) : launch<HcArgs>(e, k_hc_step<__nv_bfloat16, SC>, dim3(T), block, 0, a))
+    if (e->S <= 1) return HC_LAUNCH(1);
+    if (e->S <= 2) return HC_LAUNCH(2);
+    if (e->S <= 4) return HC_LAUNCH(4);
+    return HC_LAUNCH((int)kMaxStreams);
+#undef HC_LAUNCH
 }
 
 int sandwich(LayeredEngine *e, const float *d, const float *w_post, const float *w_pre, float *out, float *keep, uint32_t T, const float *d2 = nullptr) {
@@ -1336,7 +1341,7 @@ int embed_tokens(LayeredEngine *e, uint32_t slot, const uint32_t *tok_dev, uint3
 // logits of `nw` rows of the current chunk (want_dev holds their indices) -> e->logits [nw][V]
 int head_rows(LayeredEngine *e, uint32_t nw, const uint32_t *want_dev = nullptr) {
     if (e->form == FORM_HYPER) {
-        k_final_ln<<<nw, 256, 0, e->stream>>>(e->xs, (size_t)e->chunk_cap * e->E, e->S, want_dev ? want_dev : e->want_dev, e->final_norm, e->b_xn, e->E, e->eps);
+        k_final_ln<<<nw, nw <= kGemvMaxM && e->E >= 1024 ? 1024 : 256, 0, e->stream>>>(e->xs, (size_t)e->chunk_cap * e->E, e->S, want_dev ? want_dev : e->want_dev, e->final_norm, e->b_xn, e->E, e->eps);
         CK(cudaGetLastError());
         e->launches++;
         return gemm(e, plain(e->b_xn, e->E, e->head, e->logits, e->V, nw), 1, nw);

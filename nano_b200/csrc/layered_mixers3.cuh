@@ -31,7 +31,8 @@ struct HcArgs {
     uint32_t T, E; float eps;
     const uint32_t *tokens; const uint32_t *pos_ptr; const void *embed; float emb_scale;      // first step: streams <- embed[token] * scale
 };
-template <typename WT>
+// SC: a compile-time bound of the stream count (1, 2, 4 or kMaxStreams), so that the small loops over the streams unroll to their size
+template <typename WT, int SC>
 __global__ void __launch_bounds__(1024) k_hc_step(const HcArgs a) {
     pdl_enter();
     __shared__ float red[32];
@@ -48,11 +49,11 @@ __global__ void __launch_bounds__(1024) k_hc_step(const HcArgs a) {
     float *orow = a.out ? a.out + (size_t)t * E : nullptr;
     float sum = 0.0f;
     for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) {
-        float nx[kMaxStreams];
+        float nx[SC];
         if (erow) {
             const float v = wval(erow + i) * a.emb_scale;
 #pragma unroll
-            for (uint32_t s = 0; s < kMaxStreams; s++) nx[s] = v;
+            for (uint32_t s = 0; s < (uint32_t)SC; s++) nx[s] = v;
         } else {
             float y;
             if (a.eo) {
@@ -61,15 +62,15 @@ __global__ void __launch_bounds__(1024) k_hc_step(const HcArgs a) {
                 if (a.shared) y += a.shared[(size_t)t * E + i];
             } else y = a.y[(size_t)t * E + i];
             if (a.ls) y *= a.ls[i];
-            float old[kMaxStreams];
+            float old[SC];
 #pragma unroll
-            for (uint32_t s = 0; s < kMaxStreams; s++) old[s] = s < S ? x0[s * a.s_stride + i] : 0.0f;
+            for (uint32_t s = 0; s < (uint32_t)SC; s++) old[s] = s < S ? x0[s * a.s_stride + i] : 0.0f;
 #pragma unroll
-            for (uint32_t r = 0; r < kMaxStreams; r++) {
+            for (uint32_t r = 0; r < (uint32_t)SC; r++) {
                 float v = 0.0f;
                 if (r < S) {
 #pragma unroll
-                    for (uint32_t s = 0; s < kMaxStreams; s++) if (s < S) v = fmaf(w_mix[s * S + r], old[s], v);
+                    for (uint32_t s = 0; s < (uint32_t)SC; s++) if (s < S) v = fmaf(w_mix[s * S + r], old[s], v);
                     v = fmaf(w_out[r], y, v);
                 }
                 nx[r] = v;
@@ -77,7 +78,7 @@ __global__ void __launch_bounds__(1024) k_hc_step(const HcArgs a) {
         }
         float u = 0.0f, tot = 0.0f;
 #pragma unroll
-        for (uint32_t s = 0; s < kMaxStreams; s++)
+        for (uint32_t s = 0; s < (uint32_t)SC; s++)
             if (s < S) { x0[s * a.s_stride + i] = nx[s]; u = fmaf(w_in[s], nx[s], u); tot += nx[s]; }
         if (a.keep) a.keep[(size_t)t * E + i] = tot;
         if (orow) { orow[i] = u; sum += u; }
@@ -92,7 +93,7 @@ __global__ void __launch_bounds__(1024) k_hc_step(const HcArgs a) {
 }
 
 // out[r] = layer norm (gain w, no bias) of the sum of the streams of row want[r]
-__global__ void __launch_bounds__(256) k_final_ln(const float *__restrict__ xs, size_t s_stride, uint32_t S, const uint32_t *__restrict__ want,
+__global__ void __launch_bounds__(1024) k_final_ln(const float *__restrict__ xs, size_t s_stride, uint32_t S, const uint32_t *__restrict__ want,
                                                   const float *__restrict__ w, float *__restrict__ out, uint32_t E, float eps) {
     pdl_enter();
     __shared__ float red[32];
