@@ -2013,8 +2013,14 @@ int create(LayeredEngine *e, const nb::ModelDir *dir, uint32_t max_tokens) {
         for (const Layer &L : e->layers) if (L.type == MIX_LATENT_ATTN) mHG = std::max(mHG, (L.H + kAttnWarps - 1) / kAttnWarps);
         DM(e->b_tick, (size_t)kGemvMaxM * mHG * 4);
         CK(cudaMemset(e->b_tick, 0, (size_t)kGemvMaxM * mHG * 4));
-        if (attn_smem(mR, kAttnQT) > 48 * 1024 && (r = attn_optin<kAttnQT>((int)attn_smem(mR, kAttnQT)))) return r;
-        if (attn_smem(mR, 4) > 48 * 1024 && (r = attn_optin<4>((int)attn_smem(mR, 4)))) return r;
+        // the prefill instances by the rows they serve: kAttnQT queries per block for latents up to 256, 4 above (attn_launch)
+        uint32_t mR8 = 0, mR4 = 0;
+        for (const Layer &L : e->layers) if (L.type == MIX_LATENT_ATTN) { if (L.R <= 256) mR8 = std::max(mR8, L.RS); else mR4 = std::max(mR4, L.RS); }
+        constexpr size_t kAttnSmemMax = 227 * 1024;
+        if (std::max(attn_smem(mR8, kAttnQT), attn_smem(mR4, 4)) > kAttnSmemMax)
+            return fail(NB200_EINVAL, "a cache row of %u floats (latent + rotated key part) does not fit the attention kernel's shared memory", std::max(mR8, mR4));
+        if (mR8 && attn_smem(mR8, kAttnQT) > 48 * 1024 && (r = attn_optin<kAttnQT>((int)attn_smem(mR8, kAttnQT)))) return r;
+        if (mR4 && attn_smem(mR4, 4) > 48 * 1024 && (r = attn_optin<4>((int)attn_smem(mR4, 4)))) return r;
         if (attn_smem(mR, 1) > 48 * 1024 && (r = attn_optin<1>((int)attn_smem(mR, 1)))) return r;
     }
     if (mNE) {

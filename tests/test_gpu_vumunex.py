@@ -165,6 +165,21 @@ def test_clamps_and_score_weights_show(tmp_path):
     eng.close()
 
 
+@pytest.mark.parametrize("width,vocab", [(50, 61), (37, 33), (130, 7)])
+def test_ragged_widths(tmp_path, width, vocab):
+    """widths and vocabularies that no vector width divides, through every product of a layer"""
+    cfg = md.vumunex_config(vocab, width, [("latent_attention_2", rot(heads=3), MOE), ("latent_attention", win(heads=2, kv_rank=18), DENSE)], streams=3, scale=2.0)
+    eng, w = build(tmp_path, cfg)
+    t = toks(cfg, 45)
+    ref = O.forward(cfg, w, t)
+    assert rel(whole(eng, t), ref) < F32_TOL
+    assert rel(in_cuts(eng, t, [3, 1, 2, 4, 35]), ref) < F32_TOL
+    eng.close()
+    eng, w = build(tmp_path, cfg, f32=False, name="b")
+    assert close_bf16(whole(eng, t), ref) and close_bf16(in_cuts(eng, t, [40, 1, 1, 3]), ref)
+    eng.close()
+
+
 @pytest.mark.parametrize("streams,ls", [(None, False), (1, True), (2, False), (5, True), (8, True)])
 def test_streams_and_layer_scale(tmp_path, streams, ls):
     """no connection tensors at all (plain residual), one stream with weights, several streams; with and without the layer scale"""
