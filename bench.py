@@ -787,7 +787,7 @@ def vumunex_model(name):
     for i in range(L):
         if i % 2 == 0:
             layers.append(("latent_attention_2", {"heads": H, "dim": D, "rot_dim": RD, "vdim": VD, "kv_rank": R, "scale": (D + RD) ** -0.5,
-                                                  "rot": {"dims": RD, "base": 500000.0}}, {"kind": "dense", "ff": ff}))
+                                                  "rot": {"dims": RD, "base": 1000000.0}}, {"kind": "dense", "ff": ff}))
         else:
             layers.append(("latent_attention", {"heads": H, "dim": D, "vdim": VD, "kv_rank": R, "scale": D ** -0.5, "mask": {"size": W}}, moe))
     cfg = md.vumunex_config(FAMUDRA_VOCAB, E_, layers, streams=S, residual_mult=0.5, scale=float(E_) ** 0.5)

@@ -18,7 +18,7 @@ import vumunex_oracle as O
 
 pytestmark = pytest.mark.gpu
 
-WIN = {"heads": 3, "dim": 20, "vdim": 12, "kv_rank": 40, "scale": 0.3, "mask": {"size": 21}}
+WIN = {"heads": 3, "dim": 20, "vdim": 12, "kv_rank": 40, "scale": 0.28, "mask": {"size": 21}}
 ROT = {"heads": 5, "dim": 12, "rot_dim": 8, "vdim": 20, "kv_rank": 24, "scale": 0.35, "rot": {"dims": 8, "base": 300.0}}
 DENSE = {"kind": "dense", "ff": 56}
 MOE = {"kind": "moe", "router": {"experts": 6, "top": 2}, "expert": {"ff": 24, "limit": 1.2}, "shared": {"ff": 40, "limit": 0.8}}
@@ -121,7 +121,7 @@ MIXERS = [
     ("latent_attention_2", ROT),
     ("latent_attention_2", rot(heads=2, dim=16, rot_dim=16, vdim=16, kv_rank=16, rot={"dims": 16, "base": 10000.0})),       # sizes all equal
     ("latent_attention_2", rot(heads=3, dim=5, rot_dim=6, vdim=9, kv_rank=30, rot={"dims": 2, "base": 7.0})),               # one pair turns, the rest of the part passes
-    ("latent_attention_2", rot(heads=8, dim=32, rot_dim=32, vdim=32, kv_rank=128, scale=0.11, rot={"dims": 32, "base": 5e5})),
+    ("latent_attention_2", rot(heads=8, dim=32, rot_dim=32, vdim=32, kv_rank=128, scale=0.11, rot={"dims": 32, "base": 2e5})),
     ("latent_attention_2", rot(heads=2, dim=24, rot_dim=4, vdim=16, kv_rank=256, scale=0.2, rot={"dims": 4, "base": 50.0})),
     ("latent_attention_2", rot(heads=10, dim=3, rot_dim=2, vdim=4, kv_rank=13, rot={"dims": 2, "base": 2.0})),
 ]
