@@ -5,8 +5,8 @@
     python bench.py --impl reference ...        # the reference's own OpenMP CPU engine on the host cores
 
 A *step* is one pass of the hot path over one batch of synthetic input: a 16-token prompt is pushed through the
-token-at-a-time path (infer.c:1258-1260), then greedy decode (temperature 0, repetition penalty 1.0) runs to `seq`
-(SURVEY 8(d)).  tokens/s is counted over the decode segment only, like the reference's own TPS.
+token-at-a-time path (infer.c:1258-1260), then greedy decode (temperature 0, repetition penalty 1.0) runs to `seq`.
+tokens/s is counted over the decode segment only, like the reference's own TPS.
 
   value    : device-resident loop (nb200_decode_greedy: the token is fed back on the GPU, inputs already in HBM), decode
              segments timed with CUDA events on the launching stream, max over ranks.  No host can reach this loop through
@@ -195,7 +195,7 @@ def _cpu_run(path, spec, seq, sample_end, kind, flavour, threads, bind, runs, ti
 
 
 def cpu_sweep(path, spec, seq, budget_s=30.0):
-    """OMP_NUM_THREADS x {default, OMP_PROC_BIND=true OMP_WAIT_POLICY=active} on a short probe
+    """Thread sweep of the reference's CPU run: OMP_NUM_THREADS x {default, OMP_PROC_BIND=true OMP_WAIT_POLICY=active} on a short probe
     (README.md:73: N 'must be found by experiment'); returns the best (threads, bind) and the probe table."""
     from oracle import bindings as ob
     flavour = ob.best_fast_flavour()
@@ -235,7 +235,7 @@ def cpu_baseline(workload, path, spec, seq, runs=1):
 
 def run_reference_arm(args, workload):
     """--impl reference: the unmodified reference CPU engine on the SAME workload: every step is one full prompt + decode run
-    (tokens PROMPT..seq-1 timed), at the best thread setting of the BASELINE.md section-3 sweep; value = median over the K steps."""
+    (tokens PROMPT..seq-1 timed), at the best thread setting of that thread sweep; value = median over the K steps."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
     preset, quant, gs, seq = WORKLOADS[workload]

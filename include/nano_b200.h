@@ -92,7 +92,7 @@ int nb200_engine_create(nb200_engine **out, const uint8_t *image, uint64_t image
                         uint32_t max_seq_len, int device, uint32_t flags);
 void nb200_engine_destroy(nb200_engine *e);
 
-/* Tensor parallelism over NVLink peer memory (SURVEY 8e; the reference has no counterpart, it is one CPU
+/* Tensor parallelism over NVLink peer memory (the reference has no counterpart, it is one CPU
  * process).  Rank r of `tp_size` uploads its row slice of every matrix (whole kv-head groups for QKV and
  * attention; contiguous row ranges for O, W1|W3, W2 and the classifier) and allocates an "exchange block"
  * its peers write into.  After creation every rank must be attached to the others' blocks, either
@@ -171,7 +171,7 @@ int nb200_decode_greedy(nb200_engine *e, uint32_t *ids, uint32_t n_prompt, uint3
 int nb200_read_buffer(nb200_engine *e, int field, uint32_t layer, uint32_t pos, float *dst, uint32_t count);
 int nb200_write_x(nb200_engine *e, const float *x, uint32_t count);
 /* run exactly one transformer block on the current x at (layer,pos): layer-level parity with
- * oracle-injected inputs (SURVEY 8d check 2). */
+ * oracle-injected inputs. */
 int nb200_run_layer(nb200_engine *e, uint32_t layer, uint32_t pos, uint32_t is_causal);
 /* per-kernel-class device time (CUDA events around every launch, graph and PDL off): class ids
  * 0 embed, 1 qkv, 2 attention, 3 o-proj, 4 w1|w3, 5 w2, 6 classifier. Used by bench.py's roofline. */

@@ -7,7 +7,7 @@
                                          where they lie under /root/reference -- only when that tree exists
     nano_b200/lib/nano_cli               infer/main_cli.c linked against our libraries ("nano_cli links unchanged")
 
-The outputs are git-ignored but travel to the GPU box with the gpurun snapshot.
+The outputs are git-ignored: the history stays source-only.
 """
 from __future__ import annotations
 

@@ -8,7 +8,7 @@
  * Host code stays C and keeps the reference's semantics (same names, argument meaning, status codes and
  * exit(EXIT_FAILURE) error convention); everything on the per-token path is one call into the CUDA engine.
  * The tokenizer, maps/tries, platform_calloc and the xorshift RNG are the reference's own objects, resolved
- * at link time exactly as before (SURVEY 8b).
+ * at link time exactly as before.
  *
  * Deliberate differences (supersets of the reference's behaviour):
  *   - ctx->observation may be NULL (the reference dereferences it unconditionally: infer.c:756 ff.);

@@ -7,7 +7,7 @@
 //   epilogues ............. KV-cache store, residual add (infer.c:906,963), SwiGLU (infer.c:937),
 //                           repetition penalty + argmax (infer.c:1156-1171, 1026-1037)
 //
-// Numerics contract (DESIGN.md "Numerics"):
+// Numerics contract:
 //   * integer work (Q80 / Q4K group dots, activation codes) is exact;
 //   * exact mode (and the nb200_op_* operator entry points): every fp32 combine that follows an integer dot is
 //     evaluated in the reference's order with __fmul_rn/__fadd_rn (no FMA contraction), so a quantised matvec is
@@ -59,7 +59,7 @@ struct DevState {
 };
 
 // ------------------------------------------------------------------------------------------------
-// Tensor parallelism over NVLink peer memory (SURVEY 8e; there is no reference code for this, the reference is one CPU).
+// Tensor parallelism over NVLink peer memory (there is no reference code for this, the reference is one CPU).
 // Every rank owns a row slice of each matrix (whole kv-head groups for QKV/attention) and keeps the FULL activation
 // vectors x / xba / hb in an "exchange block" that its peers can write.  Each element of those vectors is a 64-bit word
 // {fp32 value, 32-bit epoch}: a producing kernel's epilogue pushes every finished element into every rank's copy with ONE

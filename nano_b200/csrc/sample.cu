@@ -1,4 +1,4 @@
-// sample.cu -- temperature / top-p sampling on the device (SURVEY 8(f3)).
+// sample.cu -- temperature / top-p sampling on the device.
 //
 // Reference: generate_next_token, temperature > 0 branch (infer/infer.c:1170-1189): logits /= temperature, softmax (:616-634),
 // coin = random_f32 (utils.c:959-970, drawn by the host shim from the Sampler's xorshift state), sample_top_p (:1062-1109).

@@ -1,4 +1,4 @@
-"""Export a Hugging Face Qwen3 checkpoint to a bd4sur/Nano model file (SURVEY section 8 row f1; what infer/tools/export_qwen.py:639-750
+"""Export a Hugging Face Qwen3 checkpoint to a bd4sur/Nano model file (what infer/tools/export_qwen.py:639-750
 does with its own model class): the tensors are taken from the HF state dict as they are -- the engine's `rope_qwen3`
 (infer.c:692-711) rotates the two halves of a head exactly like HF's `rotate_half`, so no q/k permutation is needed
 (export_qwen.py:694-697) -- and written in the reference's section order by `modelfile.write_model_from_weights`.

@@ -1,7 +1,7 @@
 """Export a Nano checkpoint (the reference's PyTorch `GPT`, model.py:325-417) to a Nano model file: what export.py:228-513 does
 (`export_model` F32, `export_quantized` Q80), restated over `modelfile.write_model_from_weights`.  Same header, tokenizer section,
 tensor order and Q80 arithmetic, so the output is byte-identical to the reference exporter's for the same model
-(tests/test_export_nano.py).  Format tooling (SURVEY section 8 row f1), not part of the decode hot path.
+(tests/test_export_nano.py).  Format tooling, not part of the decode hot path.
 
     python -m nano_b200.export_nano checkpoint.pt nano.bin --quant q80      # needs the reference's model.py on PYTHONPATH to unpickle
 """

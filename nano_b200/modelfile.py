@@ -1,6 +1,6 @@
 """Writer for bd4sur/Nano model files (F32 / Q80 / Q4K) with seeded synthetic weights.
 
-There are no real weights in the reference repo or in this environment (SURVEY finding 5), so every
+There are no real weights in the reference repo or in this environment, so every
 parity/bench configuration runs on synthetic weights written in the reference's on-disk format:
 
 * header + section order ........ infer/infer.c:220-320 (parse_model_file), :100-217 (memory_map_params)
@@ -13,7 +13,7 @@ parity/bench configuration runs on synthetic weights written in the reference's 
 The Q4K block quantiser here is a vectorised float32 NumPy restatement of tensor.c:144-242; tests check it
 bit-for-bit against the reference's own `quantize_tensor_q4k` (tests/test_oracle_vs_reference.py).
 
-This is format tooling (SURVEY §8 row f1), not part of the decode hot path.
+This is format tooling, not part of the decode hot path.
 """
 from __future__ import annotations
 
@@ -59,13 +59,13 @@ class ModelSpec:
         return self.hd * self.n_kv_head
 
     def n_weights(self) -> int:
-        """Quantisable weights read once per token (layers + classifier), SURVEY §8(d) `W`."""
+        """Quantisable weights read once per token (layers + classifier): the weight count `W` of the bandwidth model."""
         E, F, Q, K = self.n_embd, self.n_hidden, self.q_dim, self.kv_dim
         per_layer = Q * E + 2 * K * E + E * Q + 3 * F * E
         return self.n_layer * per_layer + self.vocab * E
 
     def bytes_per_token(self, quant: int, gs: int, pos: float) -> float:
-        """Algorithmic HBM bytes for one decoded token at position `pos` (SURVEY §8(d) formula B(p))."""
+        """Algorithmic HBM bytes for one decoded token at position `pos` (the bandwidth model's B(p))."""
         bpw = {QUANT_F32: 4.0, QUANT_Q80: 1.0 + 4.0 / max(gs, 1), QUANT_Q4K: 148.0 / 256.0}[quant]
         L, E = self.n_layer, self.n_embd
         b = self.n_weights() * bpw + 4 * E * (2 * L + 1)
@@ -121,7 +121,7 @@ def _nearest_int(v: np.ndarray) -> np.ndarray:
 def quantize_q4k_blocks(x: np.ndarray) -> np.ndarray:
     """Quantise rows of 256 floats into 160-byte Q4K blocks (tensor.c:144-242). x: [..., n], n % 256 == 0."""
     x = np.ascontiguousarray(x, dtype=np.float32)
-    assert x.shape[-1] % 256 == 0, "Q4K writer requires n % 256 == 0 (SURVEY Appendix B)"
+    assert x.shape[-1] % 256 == 0, "Q4K writer requires n % 256 == 0"
     g = x.reshape(-1, 8, 32)
     nb = g.shape[0]
     lo = np.minimum(g.min(axis=2), FLT_MAX)
@@ -216,7 +216,7 @@ def _rope_table(block: int, hd: int, theta: float = 10000.0):
 def write_model(path: str, spec: ModelSpec, quant: int, gs: int = 128, seed: int = 39,
                 cls_gain: float = 1.0, fast: bool = False) -> dict:
     """Write a synthetic model file. Weights ~ N(0, 0.02^2) (wo, w3: 0.02/sqrt(2L)), norm gains 1+N(0,0.02^2),
-    tied classifier (SURVEY §8(d)). Returns {'path','bytes','spec','quant','gs'}.
+    tied classifier. Returns {'path','bytes','spec','quant','gs'}.
     `cls_gain` scales the embedding/classifier rows (bigger top-1 margins for greedy tests)."""
     rng = np.random.default_rng(seed)
     L, E, F, V = spec.n_layer, spec.n_embd, spec.n_hidden, spec.vocab
@@ -416,7 +416,7 @@ def cached_model(spec: ModelSpec, quant: int, gs: int = 128, seed: int = 39, cac
 
 
 def teacher_tokens(n: int, vocab: int, seed: int = 39) -> np.ndarray:
-    """xorshift* stream of utils.c:959-965 (random_u32), reduced mod min(V, 151669) (SURVEY App. E.4)."""
+    """xorshift* stream of utils.c:959-965 (random_u32), reduced mod min(V, 151669)."""
     mod = min(vocab, QWEN_TOKENIZER_ENTRIES)
     st = seed & 0xFFFFFFFFFFFFFFFF
     out = np.zeros(n, dtype=np.uint32)

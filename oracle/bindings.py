@@ -1,4 +1,4 @@
-"""ctypes bindings for the CHECKERS (test infrastructure only).
+"""ctypes bindings for the oracles (test infrastructure only).
 
 * `NanoOracle`  -> oracle/libnano_oracle.so  (our C restatement, oracle/nano_oracle.c)
 * `RefEngine`   -> oracle/_ref/libnano_ref_<flavour>.so (the unmodified reference, oracle/Makefile)

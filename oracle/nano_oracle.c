@@ -2,7 +2,7 @@
  * oracle/nano_oracle.c -- TEST INFRASTRUCTURE ONLY.
  *
  * Plain-C restatement of the reference CPU engine's decode path (bd4sur/Nano infer/infer.c +
- * infer/tensor.c).  It is the CHECKER for the CUDA engine: only tests/, __graft_entry__.smoke()
+ * infer/tensor.c).  It is the oracle for the CUDA engine: only tests/, __graft_entry__.smoke()
  * and bench.py's cpu_baseline / --impl reference legs may load it.  The product libraries never
  * link or dlopen it, and there is no CPU fallback in the product.
  *
@@ -35,7 +35,7 @@
 #define NOR_Q4K_TENSOR_HDR 44
 
 /* ------------------------------------------------------------------------------------------ */
-/* unaligned little-endian readers (file sections are not aligned: SURVEY Appendix A)          */
+/* unaligned little-endian readers (file sections are not aligned)          */
 /* ------------------------------------------------------------------------------------------ */
 static inline uint32_t rd_u32(const uint8_t *p) { uint32_t v; memcpy(&v, p, 4); return v; }
 static inline uint64_t rd_u64(const uint8_t *p) { uint64_t v; memcpy(&v, p, 8); return v; }
@@ -85,7 +85,7 @@ void nor_matvec_f32(float *out, const float *x, const uint8_t *w_bytes, int n, i
 }
 
 /* tensor.c:21-46.  An all-zero group gives scale 0 and 0/0 in the reference (UB cast that yields 0
- * on x86-64); normalised to code 0 here (SURVEY Appendix B). */
+ * on x86-64); normalised to code 0 here. */
 void nor_q80_quantize(int8_t *codes, float *scales, const float *x, int n, int gs) {
     int ngroups = n / gs;
     for (int g = 0; g < ngroups; g++) {
@@ -257,7 +257,7 @@ static float q4k_block_dot(const uint8_t *p, const uint8_t *q) {
 }
 
 /* tensor.c:281-310 restricted to n % 256 == 0 or a single short line (the reference's partial-block
- * offset is only right in those cases, SURVEY Appendix B). blocks_out: nblk*160 bytes, zero-filled. */
+ * offset is only right in those cases). blocks_out: nblk*160 bytes, zero-filled. */
 void nor_q4k_quantize_rows(uint8_t *blocks_out, const float *x, uint64_t nrows, uint32_t n) {
     uint32_t bpr = (n + 255) / 256;
     #pragma omp parallel for NOR_PAR((long)nrows * n)

@@ -81,7 +81,7 @@ def main():
     np.savez_compressed(os.path.join(HERE, "lora_logits.npz"), **lora_out)
 
     # Noise floor of the reference itself: max |logit(fast build) - logit(strict build)| of the SAME source on the
-    # SAME file (SURVEY finding 11).  The fast-mode GPU tolerance is max(north-star tolerance, 1.5 x this floor).
+    # SAME file.  The fast-mode GPU tolerance is max(north-star tolerance, 1.5 x this floor).
     floors = {}
     S = 40
     for name, quant, gs in TOY_CONFIGS + [("mini-qwen3", mf.QUANT_Q80, 128), ("mini-nano", mf.QUANT_Q80, 128), ("mini-nano", mf.QUANT_Q4K, 128)]:

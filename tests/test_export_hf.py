@@ -1,4 +1,4 @@
-"""CPU test of the Hugging Face Qwen3 -> Nano model-file export (nano_b200/export_hf.py; SURVEY section 8 row f1, VERDICT r1 missing item 7).
+"""CPU test of the Hugging Face Qwen3 -> Nano model-file export (nano_b200/export_hf.py).
 There are no checkpoints in this environment, so a small randomly initialised `Qwen3ForCausalLM` stands in for one: the exported
 file is run by the oracle (and by the unmodified reference engine, when it is built here) and its logits are compared with the HF
 model's own forward pass on the same tokens.  This pins the conventions an export of real weights relies on: tensor naming and

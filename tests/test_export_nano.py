@@ -1,4 +1,4 @@
-"""CPU test of the Nano checkpoint export (nano_b200/export_nano.py; SURVEY section 8 row f1): a small randomly initialised instance of the
+"""CPU test of the Nano checkpoint export (nano_b200/export_nano.py): a small randomly initialised instance of the
 reference's own PyTorch model (model.py, imported from /root/reference in this container only) is exported by OUR exporter and by the
 reference's export.py -- the two files must be byte-identical (F32 and Q80) -- and the file's logits (oracle) must equal the PyTorch
 model's forward pass."""

@@ -1,4 +1,4 @@
-"""GPU parity on the BASELINE model shapes themselves (VERDICT r1, weak 1): Nano-168M Q80 (24 layers) and Qwen3-0.6B Q80 / Q4K
+"""GPU parity on the BASELINE model shapes themselves: Nano-168M Q80 (24 layers) and Qwen3-0.6B Q80 / Q4K
 (28 layers, V = 151 936), 40 teacher-forced positions against the strict oracle: logits within the fast-mode policy, greedy ids
 agreeing wherever the oracle's margin is real (margins printed), on the default execution path of each model.
 """
@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 
 # The floor = the reference's own -O3 -ffast-math vs strict deviation on the same file over the same 40 positions, measured with the
 # unmodified reference in the build container and committed in tests/golden/reference_noise_floor.json (Qwen3-0.6B Q4K: 0.83, with the
-# reference's two builds agreeing on only 27 of 40 greedy ids -- SURVEY finding 11 at full scale).
+# reference's two builds agreeing on only 27 of 40 greedy ids).
 CASES = [("nano-168m", mf.QUANT_Q80, 128), ("qwen3-0.6b", mf.QUANT_Q80, 128), ("qwen3-0.6b", mf.QUANT_Q4K, 128)]
 
 

@@ -51,7 +51,7 @@ def test_sort_model_logits_exact_mode(sort_model):
 
 def reference_noise_floor(name, quant, gs, path, S):
     """max|logit(reference fast build) - logit(reference strict build)| on this file: the reference's own
-    build-to-build noise (SURVEY finding 11).  Measured live when oracle/_ref travelled to this box, and never
+    build-to-build noise.  Measured live when oracle/_ref travelled to this box, and never
     below the value committed from the build container."""
     floor = json.load(open(os.path.join(GOLDEN, "reference_noise_floor.json"))).get(f"{name}_{quant:02x}_{gs}", 0.0)
     fl = ob.best_fast_flavour()
@@ -126,7 +126,7 @@ def test_matches_committed_reference_goldens(name, quant, gs):
 
 @pytest.mark.parametrize("name,quant,gs", [("toy-qwen3", mf.QUANT_Q80, 64), ("toy-nano", mf.QUANT_Q4K, 128)])
 def test_layer_level_with_injected_inputs(name, quant, gs):
-    """SURVEY 8(d) check 2: oracle x at ATTN_NORM of layer l injected into the GPU layer; outputs compared."""
+    """Oracle x at ATTN_NORM of layer l injected into the GPU layer; outputs compared."""
     spec = mf.PRESETS[name]
     path = mf.cached_model(spec, quant, gs)
     S = 12

@@ -1,4 +1,4 @@
-"""GPU parity at the BASELINE sequence lengths (VERDICT r1, weak 1): teacher-forced runs of 512 / 2048 / 4096 positions against
+"""GPU parity at the BASELINE sequence lengths: teacher-forced runs of 512 / 2048 / 4096 positions against
 the oracle on every execution path.  Two-layer models of the Nano-168M / Qwen3-0.6B layer shape keep the CPU oracle affordable;
 the attention sees exactly the shapes of the benched runs (8 kv heads, head_dim 48 / 128, up to 18 splits per kv head, several
 ring segments per split, the multi-split merge).

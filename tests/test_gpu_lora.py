@@ -1,4 +1,4 @@
-"""GPU parity tests of the LoRA plug-in path (SURVEY 8f row f4; infer.c:408-545 loader, :792-808 q/k/v branches,
+"""GPU parity tests of the LoRA plug-in path (infer.c:408-545 loader, :792-808 q/k/v branches,
 :898-903 o branch) against the unmodified reference with the same synthetic plug-in attached.
 
 Exact mode is bit-identical (logits and the V rows that received a LoRA term); fast mode is held to the north-star

@@ -1,8 +1,8 @@
-"""GPU parity tests of the tensor-parallel path (SURVEY 8e): N ranks over NVLink peer memory vs ONE GPU.
+"""GPU parity tests of the tensor-parallel path: N ranks over NVLink peer memory vs ONE GPU.
 
 Row shards compute the same per-row dot products and every rank prepares the same full activation vector, so the
 bar is bit-identity with the single-GPU multi-kernel path (which the other GPU tests pin to the oracle), plus the
-oracle comparison itself on the gathered logits.  Needs >= 2 visible GPUs (`gpurun --gpus 2`); skipped otherwise.
+oracle comparison itself on the gathered logits.  Needs >= 2 visible GPUs; skipped otherwise.
 """
 import numpy as np
 import pytest

@@ -4,7 +4,7 @@ from nano_b200 import modelfile as mf
 
 
 def test_weight_counts_match_survey():
-    # W = N168 168,296,448 / Q06 595,984,384 / Q4B 4,022,272,000
+    # weights read per token: W = N168 168,296,448 / Q06 595,984,384 / Q4B 4,022,272,000
     assert mf.PRESETS["nano-168m"].n_weights() == 168_296_448
     assert mf.PRESETS["qwen3-0.6b"].n_weights() == 595_984_384
     assert mf.PRESETS["qwen3-4b"].n_weights() == 4_022_272_000

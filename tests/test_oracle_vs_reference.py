@@ -1,6 +1,6 @@
 """CPU tests: pin the oracle (oracle/nano_oracle.c) to the reference and to the committed goldens.
 
-The reference has no test suite (SURVEY section 4); what pins behaviour is the embedded sort model
+The reference has no test suite; what pins behaviour is the embedded sort model
 (infer/main_sort.c:6-3098, README.md:379) plus outputs of the reference compiled here.
 """
 import ctypes as C

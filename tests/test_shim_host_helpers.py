@@ -1,7 +1,7 @@
 """CPU tests of the host-side framing helpers of the reference API that our shim re-implements (tensor.h:153-163):
 dequantize, parse_quantized_tensors, bytes_num_of_q4k_tensor, make_q4k_tensor, dequantize_tensor_q4k, pack_q4k_tensor,
 unpack_q4k_tensor -- called on the SAME host buffers as the unmodified reference (oracle/_ref strict build) and compared bit for
-bit.  The inputs are produced by the reference's own CPU quantisers, so no GPU is involved (VERDICT r1 rows a16 / a17)."""
+bit.  The inputs are produced by the reference's own CPU quantisers, so no GPU is involved."""
 import ctypes as C
 import os
 

@@ -26,7 +26,7 @@ b bench_q4b_q80 --workload qwen3-4b-q80 --steps 1 --warmup 1
 NB200_STREAM=0 b bench_n168_q80_multikernel --steps 2
 NB200_STREAM=1 b bench_q06_q80_stream --workload qwen3-0.6b-q80 --steps 2
 NB200_STREAM=0 b bench_q06_q4k_multikernel --workload qwen3-0.6b-q4k --steps 2
-# microbenchmarks behind the floors in DESIGN.md 5.4
+# microbenchmarks behind the latency and bandwidth floors
 for m in lat_bench bar_bench exchange_bench ring_bench consume_bench; do
   [ -x tools/micro/$m ] && (timeout 120 tools/micro/$m > $out/micro_$m.log 2>&1; tail -3 $out/micro_$m.log)
 done
@@ -48,6 +48,6 @@ PY
 # streaming kernel: launch 0 = 15 prompt positions, launch 1 = 32 decode positions (captured; ~1 minute)
 timeout 300 ncu --set full --clock-control none -k regex:k_decode_stream -s 1 -c 1 -o $out/prof_stream_n168 -f python /tmp/cap.py nano-168m q80 512 48 > $out/ncu_stream.log 2>&1
 # multi-kernel path (Qwen3-0.6B Q80): the kernels of one layer early in the decode segment (141 matching launches per token; a large
-# --launch-skip is slow under ncu, and a report of more than ~6 kernels exceeds what gpurun copies back together with the one above)
+# --launch-skip is slow under ncu, and a report of more than ~6 kernels exceeds what the GPU runner copies back together with the one above)
 NB200_STREAM=0 timeout 300 ncu --set full --clock-control none -k regex:'k_matvec|k_attention' -s 2400 -c 5 -o $out/prof_multikernel_q06 -f python /tmp/cap.py qwen3-0.6b q80 2048 40 > $out/ncu_multi.log 2>&1
 ls -la $out | tail -40
